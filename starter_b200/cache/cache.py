@@ -14,7 +14,8 @@ with one batch row per sequence and a device ``pos[batch]``
   fixed-size record per slot and layer;
 * one extra **null slot** with one null page takes the writes of padding rows.
 
-Page layout of a key/value group: ``[layer_in_group, page, kv_head, PAGE, head_dim]``.
+Page layout of a key/value group: ``[layer_in_group, page, kv_head, PAGE, head_dim]`` (values: ``v_dim`` columns,
+the same as ``head_dim`` unless the mixer asks otherwise; none at all for ``v_dim`` 0).
 Position p of a sequence lives in logical page ``p // PAGE`` at offset
 ``p % PAGE``; logical page j is physical page ``table[slot, j]`` for a full
 group and ``table[slot, j % ring_pages]`` for a window group.
@@ -35,11 +36,14 @@ PAGE = 64
 
 @dataclass(frozen=True)
 class KVRequest:
-    """A mixer's need for keys and values: every key (window None) or the last ``window``."""
+    """A mixer's need for keys and values: every key (window None) or the last ``window``.  ``v_dim``: columns of a
+    value when they differ from the key's ``head_dim``; 0 keeps no values at all (a mixer that reads its values out
+    of the cached key rows)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -76,8 +80,9 @@ class KVGroup:
         self.pool_pages = pool_pages
         self.null_page = pool_pages
         shape = (len(self.layers), pool_pages + 1, request.num_kv_heads, PAGE, request.head_dim)
+        self.v_dim = request.head_dim if request.v_dim is None else int(request.v_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:-1] + (self.v_dim,), dtype=dtype, device=device) if self.v_dim else None
         self.pages = IndexAllocator(pool_pages, "cache page")
         self.table_host = torch.full((n_slots + 1, self.table_width), -1, dtype=torch.int32)
         self.table_host[n_slots, :] = self.null_page
@@ -124,7 +129,7 @@ class KVGroup:
         return self.pool_pages * PAGE
 
     def nbytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + (self.v.numel() if self.v is not None else 0)) * self.k.element_size()
 
 
 class StateGroup:
@@ -157,8 +162,8 @@ class LayerCache:
         return self.group.k[self.index]
 
     @property
-    def v(self) -> torch.Tensor:
-        return self.group.v[self.index]
+    def v(self) -> Optional[torch.Tensor]:
+        return self.group.v[self.index] if self.group.v is not None else None
 
     @property
     def state(self) -> torch.Tensor:

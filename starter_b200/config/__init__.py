@@ -2,8 +2,10 @@
 
 from .registry import (ConfigError, ModelConfig, TensorNames, architecture_names, config_from_dict, load_config,
                        register_architecture, save_config)
-from .specs import AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec, RopeSpec
+from .specs import (AttentionSpec, BiasedAttentionSpec, BlockSpec, GatedMLPSpec, GroupedNormSpec, LatentAttentionSpec,
+                    ModelSpec, NormSpec, PairRopeSpec, ParallelBlockSpec, RopeSpec, WKVSpec)
 
 __all__ = ["ConfigError", "ModelConfig", "TensorNames", "architecture_names", "config_from_dict", "load_config",
            "register_architecture", "save_config", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
-           "NormSpec", "RopeSpec"]
+           "NormSpec", "RopeSpec", "BiasedAttentionSpec", "GroupedNormSpec", "LatentAttentionSpec", "PairRopeSpec",
+           "ParallelBlockSpec", "WKVSpec"]

@@ -1,6 +1,7 @@
 """One registry from an architecture's name to its typed configuration.
 
-``config.json`` names its architecture in ``architectures[0]``; that name picks
+``config.json`` names its architecture in ``architectures[0]`` (or in a string
+``architecture``); that name picks
 the configuration class, and the class says how the model is put together
 (``model_spec``) and what its tensors are called in a checkpoint
 (``tensor_names``).  The reference hard-wires one model
@@ -67,6 +68,8 @@ def architecture_names() -> List[str]:
 
 def config_from_dict(raw: dict) -> ModelConfig:
     names = raw.get("architectures")
+    if isinstance(raw.get("architecture"), str) and names is None:
+        names = [raw["architecture"]]     # some configurations name their one architecture in a string
     if not isinstance(names, list) or not names:
         raise ConfigError("config.json has no 'architectures' list; known architectures: "
                           + ", ".join(architecture_names()))

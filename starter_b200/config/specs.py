@@ -33,6 +33,27 @@ class RopeSpec:
 
 
 @dataclass(frozen=True)
+class GroupedNormSpec:
+    """Root-mean-square norm in groups: the last axis is cut into ``groups`` equal consecutive parts, each divided by
+    its own sqrt(mean(part^2) + eps); then the whole is multiplied by w.  One group is the plain norm."""
+
+    size: int
+    eps: float
+    groups: int = 1
+    kind: str = "grouped_rmsnorm"
+
+
+@dataclass(frozen=True)
+class PairRopeSpec:
+    """Rotary position encoding over neighbouring columns: (2j, 2j + 1) of the first ``rotary_dim`` columns turn
+    by angle(p, j) = p * theta**(-2j / rotary_dim); angles, sines and the rotation itself are 32-bit."""
+
+    theta: float
+    rotary_dim: int
+    kind: str = "rope_pairs"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention over a key/value cache.
 
@@ -54,12 +75,82 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class BiasedAttentionSpec:
+    """Causal grouped-query attention whose scores carry more than a scale, over keys of ``head_dim`` and values of
+    ``v_dim`` columns (kind "biased_attention").  Every option is off when None:
+
+    * ``value_norm_eps``: each head's value is divided by its root mean square before it is cached;
+    * ``head_temperature``: a learned number per query head multiplies the scaled score;
+    * ``slope_log2``: c takes slope_h * (i - j) off the score of query i and key j, slope_h = 2**(-c (h + 1) / heads);
+    * ``chunk``: key j is visible to query i only if i // chunk == j // chunk (counted from the sequence's start);
+    * ``window``: only the last ``window`` keys are visible.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_dim: int
+    scale: float
+    value_norm_eps: Optional[float] = None
+    head_temperature: bool = False
+    slope_log2: Optional[float] = None
+    chunk: Optional[int] = None
+    window: Optional[int] = None
+    kind: str = "biased_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention through low-rank latents (kind "latent_attention").
+
+    Queries: RMSNorm(W_dq h) of ``q_rank`` columns, up-projected to ``num_heads`` heads of [head_dim plain | rot_dim
+    rotated] columns.  Keys and values: W_dkv h gives ``kv_rank`` columns that are normed (the latent) and ``rot_dim``
+    more that are rotated and shared by all heads; a head's plain key and its value (``v_dim`` columns) are
+    up-projections of the latent.  Only the latent and the rotated part are cached.  ``sink``: the softmax's
+    denominator holds one more term exp(s_h), a learned number per head with no key or value.
+    """
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    v_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: Optional[Any] = None
+    sink: bool = False
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class WKVSpec:
+    """Linear recurrence with a [head_dim, head_dim] state per head and a data-dependent decay per key channel
+    (kind "wkv"); ``decay_rank`` is the inner size of the decay's two small matrices, ``norm_eps`` the eps of the
+    per-head unit norm of the output."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    decay_rank: int
+    norm_eps: float
+    kind: str = "wkv"
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
-    """Dense gated feed-forward: down(act(gate(x)) * up(x))."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)).
+
+    ``activation`` "silu": silu(g) * u.  "clamped_swish": g' = min(g, limit), u' = clamp(u, -limit, limit),
+    g' * sigmoid(alpha * g') * (u' + 1)."""
 
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
+    limit: Optional[float] = None
+    alpha: float = 1.702
     kind: str = "gated_mlp"
 
 
@@ -75,6 +166,16 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class ParallelBlockSpec:
+    """One layer with a single norm that both branches read: x += mixer(norm(x)) + ff(norm(x)); ``ff`` may be None."""
+
+    norm: Any
+    mixer: Any
+    ff: Any = None
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     """A decoder: embedding, layers, the order they run in, final norm, output head.
 
@@ -85,6 +186,9 @@ class ModelSpec:
     Three optional constants of the outer model, None where an architecture has none (Qwen3 has
     none): ``embedding_scale`` multiplies the embedded rows, ``logit_scale`` the logits, and
     ``logit_softcap`` c turns a logit x into c * tanh(x / c), after the scale.
+
+    ``residual_float32``: the residual stream is kept and summed in 32-bit also in a bfloat16 run (the norms then
+    read 32-bit rows and hand the run's dtype to the branches).
     """
 
     hidden_size: int
@@ -96,6 +200,7 @@ class ModelSpec:
     embedding_scale: Optional[float] = None
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
+    residual_float32: bool = False
 
     def execution_order(self) -> Tuple[int, ...]:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

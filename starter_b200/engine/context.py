@@ -87,9 +87,13 @@ class ResidualStream:
             return norm.forward(self.x)
         delta, self.pending = self.pending, None
         self.stats = None   # x changes here
+        if isinstance(delta, tuple):   # a layer whose branches run side by side left more than one output
+            return norm.add_forward(self.x, *delta)
         return norm.add_forward(self.x, delta)
 
-    def push(self, branch_output: torch.Tensor) -> None:
+    def push(self, branch_output: torch.Tensor, *more: torch.Tensor) -> None:
+        """Leave a branch's output to be added by the next norm; several outputs (branches that read the same
+        normed rows) wait together and need a norm whose ``add_forward`` takes them all."""
         if self.pending is not None:
             raise RuntimeError("a branch output is already waiting to be added to the residual")
-        self.pending = branch_output
+        self.pending = (branch_output, *more) if more else branch_output

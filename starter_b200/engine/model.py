@@ -57,6 +57,8 @@ class DecoderModel:
     def from_folder(cls, folder, runtime: Runtime) -> "DecoderModel":
         config = load_config(folder)
         checkpoint = Checkpoint.open(folder)
+        if hasattr(config, "with_shapes"):   # an architecture some of whose sizes only the tensors' shapes give
+            config = config.with_shapes(checkpoint.shapes())
         try:
             model = cls(config.model_spec(), config.tensor_names(), checkpoint, runtime)
         finally:
@@ -108,7 +110,10 @@ class DecoderModel:
 
     def hidden(self, ctx: StepContext, tokens: torch.Tensor) -> ResidualStream:
         """Run the step's rows through every layer; returns the residual stream before the final norm."""
-        x = ctx.ops.embed(tokens, self.embedding, ctx.status)
+        if self.spec.residual_float32 and self.embedding.dtype != torch.float32:
+            x = ctx.ops.embed(tokens, self.embedding, ctx.status, out_float32=True)   # the residual stays 32-bit
+        else:
+            x = ctx.ops.embed(tokens, self.embedding, ctx.status)
         if self.spec.embedding_scale is not None:
             x = (x.float() * self.spec.embedding_scale).to(x.dtype)
         stream = ResidualStream(x)
@@ -120,10 +125,11 @@ class DecoderModel:
         """32-bit logits [len(rows), vocab] at the given rows (all rows when None)."""
         ops = ctx.ops
         x, delta = stream.x, stream.pending
+        deltas = () if delta is None else (delta if isinstance(delta, tuple) else (delta,))
         if rows is not None:
             x = ops.gather_rows(x, rows)
-            delta = ops.gather_rows(delta, rows) if delta is not None else None
-        h = self.final_norm.add_forward(x, delta) if delta is not None else self.final_norm.forward(x)
+            deltas = tuple(ops.gather_rows(d, rows) for d in deltas)
+        h = self.final_norm.add_forward(x, *deltas) if deltas else self.final_norm.forward(x)
         logits = ops.linear(h, self.lm_head, out_float32=True)
         if self.spec.logit_scale is not None:
             logits = logits * self.spec.logit_scale

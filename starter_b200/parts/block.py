@@ -55,4 +55,35 @@ class PreNormBlock:
         self._branch(ctx, stream, self.ff_norm, self.ff)
 
 
+class ParallelBlock:
+    """Kind "parallel": one norm, read by the mixer and by the feed-forward; x += mixer(n) + ff(n).  Both outputs
+    wait on the residual stream and are added, in the residual's own type, by the next norm.  ``ff`` may be absent."""
+
+    @staticmethod
+    def sub_parts(spec):
+        parts = (("norm", "norm", spec.norm), ("mixer", "mixer", spec.mixer))
+        return parts + ((("ff", "ff", spec.ff),) if spec.ff is not None else ())
+
+    def __init__(self, spec, weights, runtime):
+        self.ff = None
+        for name, category, sub in self.sub_parts(spec):
+            setattr(self, name, build_part(category, sub, weights[name], runtime))
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def prepare(self, cache) -> None:
+        self.mixer.prepare(cache)
+        if self.ff is not None:
+            self.ff.prepare(cache)
+
+    def forward(self, ctx, stream, layer_cache) -> None:
+        n = stream.normed(self.norm)
+        outputs = [self.mixer.forward(ctx, n, layer_cache)]
+        if self.ff is not None:
+            outputs.append(self.ff.forward(ctx, n))
+        stream.push(*outputs)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward (kind "gated_mlp"): down(silu(gate(x)) * up(x)).
+"""Dense gated feed-forward (kind "gated_mlp"): down(silu(gate(x)) * up(x)), or with the activation
+"clamped_swish" down(g * sigmoid(alpha g) * (u + 1)) for g = min(gate(x), limit), u = clamp(up(x), -limit, limit).
 
 The reference fuses gate and up into one [2I, H] matrix, gate half first
 (engine/model.py:116, engine/kernels/swiglu.py:5-6), and rounds gate, up,
@@ -22,14 +23,19 @@ class GatedMLP:
         }
 
     def __init__(self, spec, weights, runtime):
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not built; only 'silu' is")
+        if spec.activation not in ("silu", "clamped_swish"):
+            raise ValueError(f"activation {spec.activation!r} is not built; 'silu' and 'clamped_swish' are")
+        self.activation = spec.activation
+        if self.activation == "clamped_swish":
+            if spec.limit is None or not spec.limit > 0:
+                raise ValueError("the clamped activation needs a positive limit")
+            self.limit, self.alpha = float(spec.limit), float(spec.alpha)
         self.hidden_size = spec.hidden_size
         self.intermediate_size = spec.intermediate_size
         self.ops = runtime.ops
         self.w_gate_up = self.ops.prepare_matrix(torch.cat([weights["gate"], weights["up"]], dim=0), halves=2)
         self.w_down = self.ops.prepare_matrix(weights["down"])
-        self.takes_fold = spec.hidden_size % 8 == 0 and spec.intermediate_size % 8 == 0
+        self.takes_fold = self.activation == "silu" and spec.hidden_size % 8 == 0 and spec.intermediate_size % 8 == 0
 
     def prepare(self, cache) -> None:
         pass
@@ -37,6 +43,9 @@ class GatedMLP:
     def forward(self, ctx, h, norm=None, residual=None):
         """h is the normed input; with ``norm`` it is the residual itself and the norm is taken inside the first
         product; with ``residual`` the result is added to that tensor instead of being returned on its own."""
+        if self.activation == "clamped_swish":
+            act = self.ops.gated_clamp(self.ops.linear(h, self.w_gate_up), self.alpha, self.limit)
+            return self.ops.linear(act, self.w_down)
         if norm is None and residual is None:
             return self.ops.linear(self.ops.linear_swiglu(h, self.w_gate_up), self.w_down)
         act = self.ops.linear_swiglu(h, self.w_gate_up, norm=norm)

@@ -34,4 +34,32 @@ class RMSNorm:
         return (self.weight, self.eps) if self.weight.dtype == dtype else None
 
 
+class GroupedRMSNorm:
+    """Kind "grouped_rmsnorm": the row is cut into ``groups`` equal consecutive parts and each is divided by its own
+    root mean square; all of it 32-bit, rounded once when the result is stored.  It reads rows of the residual's type
+    (32-bit when the model keeps its residual so) and hands out rows of the run's dtype."""
+
+    @staticmethod
+    def weight_shapes(spec):
+        return {"weight": (spec.size,)}
+
+    def __init__(self, spec, weights, runtime):
+        if spec.groups < 1 or spec.size % spec.groups:
+            raise ValueError(f"a norm over {spec.size} columns cannot have {spec.groups} equal groups")
+        self.size = spec.size
+        self.groups = int(spec.groups)
+        self.eps = float(spec.eps)
+        self.weight = weights["weight"]
+        self.ops = runtime.ops
+        self.dtype = runtime.dtype
+
+    def forward(self, x):
+        return self.ops.grouped_rmsnorm(x, (), self.weight, self.groups, self.eps, self.dtype)
+
+    def add_forward(self, x, *deltas):
+        """x += sum of the deltas, in place and in 32-bit (the deltas are summed first), then the norm of the new x."""
+        return self.ops.grouped_rmsnorm(x, tuple(deltas), self.weight, self.groups, self.eps, self.dtype)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

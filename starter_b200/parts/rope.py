@@ -44,4 +44,26 @@ class RotaryEmbedding:
         return self.cos, self.sin, self.rotary_dim
 
 
+class PairRotary:
+    """Kind "rope_pairs": neighbouring columns (2j, 2j + 1) turn together.  It keeps no table of sines: the kernels
+    that rotate take the row's position from the step's batch, multiply it in 32-bit with the frequency
+    theta**(-2j / rotary_dim) from ``frequencies`` (32-bit, [rotary_dim / 2]) and take sine and cosine there."""
+
+    @staticmethod
+    def weight_shapes(spec):
+        return {}
+
+    def __init__(self, spec, weights, runtime):
+        if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
+            raise ValueError(f"rotary_dim must be positive and even, got {spec.rotary_dim}")
+        self.theta = float(spec.theta)
+        self.rotary_dim = int(spec.rotary_dim)
+        j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
+        self.frequencies = (torch.tensor(self.theta, dtype=torch.float32) ** (-2.0 * j / self.rotary_dim)).to(runtime.device)
+
+    def prepare(self, n_positions: int) -> None:
+        pass
+
+
 register_part("position", "rope", RotaryEmbedding)
+register_part("position", "rope_pairs", PairRotary)

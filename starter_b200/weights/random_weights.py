@@ -39,12 +39,17 @@ class RandomSource:
         self.dtype = dtype
         self.device = torch.device(device)
         self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...]]] = {n: (dtype, s) for n, s in required.items()}
+        # an architecture may say how a tensor is filled: random_init(name, shape) -> (mean, standard deviation)
+        self.init = getattr(config, "random_init", None)
 
     def get(self, name: str) -> torch.Tensor:
         _, shape = self.entries[name]
         gen = torch.Generator(device=self.device)
         gen.manual_seed(_tensor_seed(self.seed, name))
         noise = torch.randn(shape, generator=gen, dtype=torch.float32, device=self.device)
+        if self.init is not None:
+            mean, std = self.init(name, shape)
+            return (mean + std * noise).to(self.dtype)
         if len(shape) == 1:
             return (1.0 + NORM_STD * noise).to(self.dtype)
         return (MATRIX_STD * noise).to(self.dtype)

@@ -28,11 +28,150 @@ class EmulatedOps:
 
     # ---- rows ---------------------------------------------------------------------------
 
-    def embed(self, tokens, table, status):
+    def embed(self, tokens, table, status, out_float32=False):
         bad = (tokens < 0) | (tokens >= table.shape[0])
         if bool(bad.any()):
             status |= 1
-        return table[tokens.long().clamp(0, table.shape[0] - 1)].clone()
+        out = table[tokens.long().clamp(0, table.shape[0] - 1)].clone()
+        return out.float() if out_float32 else out
+
+    def grouped_rmsnorm(self, x, deltas, w, groups, eps, out_dtype):
+        if deltas:
+            total = deltas[0].float()
+            for d in deltas[1:]:
+                total = total + d.float()
+            x.copy_((x.float() + total).to(x.dtype))
+        parts = x.float().reshape(x.shape[0], groups, -1)
+        n = parts * torch.rsqrt((parts * parts).mean(-1, keepdim=True) + eps)
+        return (n.reshape(x.shape) * w.float()).to(out_dtype)
+
+    def gated_clamp(self, gu, alpha, limit):
+        inter = gu.shape[1] // 2
+        g = gu[:, :inter].float().clamp(max=limit)
+        u = gu[:, inter:].float().clamp(min=-limit, max=limit)
+        return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+    def tanh(self, x):
+        return torch.tanh(x.float()).to(x.dtype)
+
+    def linear_heads(self, a, w, out):
+        out.copy_(torch.einsum("rhk,hnk->rhn", a.float(), w.float()).to(out.dtype))
+        return out
+
+    @staticmethod
+    def _turn(t, pos, freqs, rot):
+        """t [rows, heads, R] with its first ``rot`` columns rotated in neighbouring pairs."""
+        if freqs is None or not rot:
+            return t.clone()
+        angle = pos.float()[:, None] * freqs.float()[None, :]
+        c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        a, b = t[..., 0:rot:2], t[..., 1:rot:2]
+        out = t.clone()
+        out[..., 0:rot:2] = a * c - b * s
+        out[..., 1:rot:2] = b * c + a * s
+        return out
+
+    def rotate_pairs(self, ctx, src, dst, freqs, rot):
+        _, pos = self._positions(ctx)
+        dst.copy_(self._turn(src.float(), pos, freqs, rot).to(dst.dtype))
+
+    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot):
+        dt = down.dtype
+        slots, pos = self._positions(ctx)
+        d = down.float()
+
+        def unit(t):
+            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
+
+        cq = (unit(d[:, :q_rank]) * q_norm.float()).to(dt)
+        latent = unit(d[:, q_rank:q_rank + kv_rank]) * kv_norm.float()
+        shared = self._turn(d[:, None, q_rank + kv_rank:], pos, freqs, rot)[:, 0]
+        page, off = self._physical(layer_cache.group, slots, pos)
+        if bool((page < 0).any()):
+            ctx.status |= 2
+        ok = page >= 0
+        layer_cache.k[page[ok], 0, off[ok]] = torch.cat([latent, shared], dim=-1)[ok].to(dt)
+        return cq
+
+    def kv_store(self, ctx, k, v, layer_cache, value_norm_eps):
+        group = layer_cache.group
+        G, D, V = group.request.num_kv_heads, group.request.head_dim, group.v_dim
+        slots, pos = self._positions(ctx)
+        vv = v.float().reshape(-1, G, V)
+        if value_norm_eps is not None:
+            vv = vv * torch.rsqrt((vv * vv).mean(-1, keepdim=True) + value_norm_eps)
+        page, off = self._physical(group, slots, pos)
+        if bool((page < 0).any()):
+            ctx.status |= 2
+        ok = page >= 0
+        layer_cache.k[page[ok], :, off[ok]] = k.reshape(-1, G, D)[ok].to(layer_cache.k.dtype)
+        layer_cache.v[page[ok], :, off[ok]] = vv[ok].to(layer_cache.v.dtype)
+
+    def flex_attention(self, ctx, q, layer_cache, scale, v_dim, values_in_keys=False, sink=None, head_scale=None, slopes=None,
+                       chunk=None, window=None):
+        group = layer_cache.group
+        M, H, dt = q.shape[0], q.shape[1], q.dtype
+        G = group.request.num_kv_heads
+        slots, pos = self._positions(ctx)
+        out = torch.empty(M, H * v_dim, dtype=dt, device=q.device)
+        qf = q.float()
+        for r in range(M):
+            p = int(pos[r])
+            lo = 0
+            if window is not None:
+                lo = max(lo, p - window + 1)
+            if chunk is not None:
+                lo = max(lo, (p // chunk) * chunk)
+            keys = torch.arange(lo, p + 1, device=q.device)
+            page, off = self._physical(group, slots[r].expand(keys.numel()), keys)
+            kk = layer_cache.k[page, :, off].float()                               # [n, G, Kd]
+            vv = kk[..., :v_dim] if values_in_keys else layer_cache.v[page, :, off].float()
+            kk, vv = kk.repeat_interleave(H // G, dim=1), vv.repeat_interleave(H // G, dim=1)
+            s = torch.einsum("hd,nhd->hn", qf[r], kk) * scale
+            if head_scale is not None:
+                s = s * head_scale.float()[:, None]
+            if slopes is not None:
+                s = s - slopes.float()[:, None] * (p - keys).float()[None, :]
+            top = s.max(dim=-1, keepdim=True).values
+            if sink is not None:
+                top = torch.maximum(top, sink.float()[:, None])
+            e = torch.exp(s - top)
+            total = e.sum(-1, keepdim=True)
+            if sink is not None:
+                total = total + torch.exp(sink.float()[:, None] - top)
+            out[r] = (torch.einsum("hn,nhd->hd", e, vv) / total).reshape(-1).to(dt)
+        return out
+
+    def token_shift(self, ctx, h, state, prev_offset, mu):
+        slots = ctx.seq_slot.long()[ctx.row_seq.long()]
+        first = ctx.cu_q.long()[ctx.row_seq.long()]
+        rows = torch.arange(ctx.n_rows, device=h.device)
+        hf = h.float()
+        before = torch.where((rows == first)[:, None], state[slots, prev_offset:prev_offset + h.shape[1]].float(),
+                             hf[(rows - 1).clamp(min=0)])
+        return (hf[None] + (before - hf)[None] * mu.float()[:, None, :]).to(h.dtype)
+
+    def wkv_scan(self, ctx, r, k, v, g, decay_pre, w0, u, norm, eps, h, state, heads, dim, prev_offset):
+        H, D = heads, dim
+        out = torch.empty(r.shape[0], H * D, dtype=torch.float32, device=r.device)
+        cu = ctx.cu_q.tolist()
+        decay = torch.exp(-torch.exp(decay_pre.float() + w0.float())).reshape(-1, H, D)
+        rr, kk, vv = (t.float().reshape(-1, H, D) for t in (r, k, v))
+        uu = u.float().reshape(H, D)
+        for b in range(ctx.n_seqs):
+            slot = int(ctx.seq_slot[b])
+            S = state[slot, :prev_offset].reshape(H, D, D).clone()
+            for t in range(cu[b], cu[b + 1]):
+                kv = kk[t][:, :, None] * vv[t][:, None, :]
+                out[t] = torch.einsum("hk,hkv->hv", rr[t], S + uu[:, :, None] * kv).reshape(-1)
+                S = decay[t][:, :, None] * S + kv
+            state[slot, :prev_offset] = S.reshape(-1)
+            if cu[b + 1] > cu[b]:
+                state[slot, prev_offset:prev_offset + h.shape[1]] = h[cu[b + 1] - 1].float()
+        o = out.reshape(-1, H, D)
+        o = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)).reshape(-1, H * D)
+        gf = g.float()
+        return (o * norm.float() * (gf * torch.sigmoid(gf))).to(r.dtype)
 
     def gather_rows(self, x, rows):
         return x[rows.long()].clone()

@@ -69,7 +69,8 @@ def poison_cache(sess):
     for g in sess.cache.groups:
         if hasattr(g, "k"):
             g.k.fill_(float("nan"))
-            g.v.fill_(float("nan"))
+            if g.v is not None:
+                g.v.fill_(float("nan"))
 
 
 def run_ragged_batches(sess, seqs, batch_size, prefix_fraction=0.5, poison=False):
