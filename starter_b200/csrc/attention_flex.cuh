@@ -1,0 +1,49 @@
+// What the kernels of attention_flex*.cu share: the description of one attention call and of the cache it reads.
+#pragma once
+#include "common.cuh"
+
+#define FLEX_MAX_V 512   // widest value row of the general kernel
+
+// q is a view [rows, heads, k_dim] with a row stride and a head stride (elements).  Keys: pages
+// [page][kv_head][SB_PAGE][k_dim].  Values: pages [page][kv_head][SB_PAGE][v_row] of which the first v_dim columns
+// count; for values kept inside the key rows v points at k and v_row is k_dim.  head_scale, slopes and sink are
+// 32-bit per query head, null when the option is off; window and chunk are 0 when off.
+struct SbFlex {
+    const void* q;
+    long long q_row;
+    long long q_head;
+    void* k;
+    void* v;
+    const int* table;
+    const float* head_scale;
+    const float* slopes;
+    const float* sink;
+    int table_width;
+    int ring_pages;
+    int n_heads;
+    int n_kv_heads;
+    int k_dim;
+    int v_dim;
+    int v_row;
+    int window;
+    int chunk;
+    float scale;
+};
+
+// First visible key of a query at position pos.
+__device__ __forceinline__ int flex_first_key(const SbFlex& p, int pos) {
+    int lo = 0;
+    if (p.window > 0) lo = max(lo, pos - p.window + 1);
+    if (p.chunk > 0) lo = max(lo, (pos / p.chunk) * p.chunk);
+    return lo;
+}
+
+// Index of [page][kv_head][pos % SB_PAGE] among a layer's token rows, or -1 when the slot has no page there.
+__device__ __forceinline__ long long flex_token(const SbFlex& p, int slot, int pos, int kv_head) {
+    int lp = pos / SB_PAGE;
+    if (p.ring_pages) lp %= p.ring_pages;
+    if (lp >= p.table_width) return -1;
+    const int page = p.table[(long long)slot * p.table_width + lp];
+    if (page < 0) return -1;
+    return ((long long)page * p.n_kv_heads + kv_head) * SB_PAGE + (pos % SB_PAGE);
+}

@@ -44,6 +44,13 @@ class SbFusedQK(Structure):
                 ("next_w", c_void_p), ("next_bytes", c_longlong)]
 
 
+class SbFlex(Structure):
+    _fields_ = [("q", c_void_p), ("q_row", c_longlong), ("q_head", c_longlong), ("k", c_void_p), ("v", c_void_p),
+                ("table", c_void_p), ("head_scale", c_void_p), ("slopes", c_void_p), ("sink", c_void_p),
+                ("table_width", c_int), ("ring_pages", c_int), ("n_heads", c_int), ("n_kv_heads", c_int), ("k_dim", c_int),
+                ("v_dim", c_int), ("v_row", c_int), ("window", c_int), ("chunk", c_int), ("scale", c_float)]
+
+
 def _code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return F32
@@ -96,6 +103,23 @@ class Ops:
                                               c_void_p, c_void_p],
             "sb_attn_decode_fused": [SbFusedQK, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p],
+            "sb_embed_wide": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+            "sb_grouped_rmsnorm": [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                   c_float, c_void_p],
+            "sb_gated_clamp": [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+            "sb_tanh": [c_int, c_void_p, c_void_p, c_longlong, c_void_p],
+            "sb_gemm_heads": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
+                              c_int, c_int, c_void_p],
+            "sb_flex_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_void_p],
+            "sb_kv_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, SbBatch, SbFlex, c_int, c_float, c_void_p, c_void_p],
+            "sb_rotate_pairs": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, SbBatch, c_void_p,
+                                c_int, c_int, c_int, c_void_p],
+            "sb_latent_prepare": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbFlex, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_float, c_void_p, c_int, c_void_p, c_void_p],
+            "sb_token_shift": [c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, SbBatch, c_int, c_void_p,
+                               c_void_p],
+            "sb_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                            c_void_p, c_int, c_void_p, c_longlong, c_int, SbBatch, c_int, c_int, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p],
@@ -197,7 +221,14 @@ class Ops:
 
     # ---- rows ---------------------------------------------------------------------------
 
-    def embed(self, tokens, table, status):
+    def embed(self, tokens, table, status, out_float32=False):
+        """Rows of the table by token id; ``out_float32``: a bfloat16 table's rows widened to 32-bit (for a model
+        whose residual stream is 32-bit in every run)."""
+        if out_float32 and table.dtype == torch.bfloat16:
+            out = torch.empty((tokens.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+            self._check(self.lib.sb_embed_wide(_ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0], table.shape[1],
+                                               table.shape[0], _ptr(status), self._stream()), "embed_wide")
+            return out
         out = torch.empty((tokens.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
         self._check(self.lib.sb_embed(_code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0],
                                       table.shape[1], table.shape[0], _ptr(status), self._stream()), "embed")
@@ -226,6 +257,40 @@ class Ops:
         out = torch.empty_like(x)
         self._check(self.lib.sb_rmsnorm(dt, wdt, _ptr(x), _ptr(delta), _ptr(w), _ptr(out), x.shape[0], x.shape[1], eps,
                                         self._stream()), "add_rmsnorm")
+        return out
+
+    def grouped_rmsnorm(self, x, deltas, w, groups, eps, out_dtype):
+        """RMSNorm of x's rows in ``groups`` equal consecutive parts, times w, in ``out_dtype``.  With ``deltas`` (one or
+        two tensors of ``out_dtype``) x += their sum first, in place and in x's own type; x may be 32-bit in a
+        bfloat16 run."""
+        if len(deltas) > 2:
+            raise KernelError("the grouped norm adds up to two branch outputs")
+        if x.dtype == torch.bfloat16 and out_dtype != torch.bfloat16:
+            raise KernelError("bfloat16 rows are normed into bfloat16")
+        if out_dtype == torch.float32 and w.dtype != torch.float32:
+            raise KernelError("a float32 run needs float32 norm weights")
+        for d in deltas:
+            if d.dtype != out_dtype or d.shape != x.shape or not d.is_contiguous():
+                raise KernelError("a branch output has the run's dtype and the residual's shape")
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        d1 = deltas[0] if deltas else None
+        d2 = deltas[1] if len(deltas) > 1 else None
+        self._check(self.lib.sb_grouped_rmsnorm(_code(x.dtype), _code(out_dtype), _code(w.dtype), _ptr(x), _ptr(d1), _ptr(d2),
+                                                _ptr(w), _ptr(out), x.shape[0], x.shape[1], int(groups), float(eps),
+                                                self._stream()), "grouped_rmsnorm")
+        return out
+
+    def gated_clamp(self, gu, alpha, limit):
+        """[g | u] -> g' * sigmoid(alpha g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)."""
+        inter = gu.shape[1] // 2
+        out = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
+        self._check(self.lib.sb_gated_clamp(_code(gu.dtype), _ptr(gu), _ptr(out), gu.shape[0], inter, float(alpha), float(limit),
+                                            self._stream()), "gated_clamp")
+        return out
+
+    def tanh(self, x):
+        out = torch.empty_like(x)
+        self._check(self.lib.sb_tanh(_code(x.dtype), _ptr(x), _ptr(out), x.numel(), self._stream()), "tanh")
         return out
 
     def swiglu(self, gu):
@@ -634,6 +699,133 @@ class Ops:
         self._check(self.lib.sb_attention_general(_code(q.dtype), _ptr(q), _ptr(out), self._batch(ctx), kv,
                                                   n_heads, scale, int(window or 0), self._stream()), "attention_general")
         return out
+
+    # ---- attention with options, latents, the linear recurrence --------------------------
+
+    def linear_heads(self, a, w, out):
+        """out[m, h, :] = a[m, h, :] times w[h] transposed, for views a [rows, heads, K] and out [rows, heads, N] whose
+        last axis is contiguous (a head's columns inside wider rows) and w [heads, N, K]."""
+        rows, H, K = a.shape
+        N = w.shape[1]
+        if (tuple(w.shape) != (H, N, K) or tuple(out.shape) != (rows, H, N) or a.stride(2) != 1 or out.stride(2) != 1
+                or not w.is_contiguous() or not (a.dtype == w.dtype == out.dtype)):
+            raise KernelError(f"linear_heads: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.sb_gemm_heads(_code(a.dtype), _ptr(a), a.stride(0), a.stride(1), _ptr(w), _ptr(out), out.stride(0),
+                                           out.stride(1), rows, N, K, H, self._stream()), "gemm_heads")
+        return out
+
+    def _flex(self, layer_cache, q=None, n_heads=0, scale=1.0, v_dim=None, values_in_keys=False, sink=None, head_scale=None,
+              slopes=None, chunk=None, window=None) -> SbFlex:
+        g = layer_cache.group
+        k = layer_cache.k
+        if values_in_keys:
+            v, v_row = k, g.request.head_dim
+            v_dim = g.request.head_dim if v_dim is None else v_dim
+        else:
+            v, v_row = layer_cache.v, g.v_dim
+            v_dim = g.v_dim if v_dim is None else v_dim
+            if v is None or v_dim != g.v_dim:
+                raise KernelError("the layer's cache keeps no values of this width")
+        if v_dim > v_row:
+            raise KernelError("values wider than the rows they are read from")
+        for t in (sink, head_scale, slopes):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n_heads or not t.is_contiguous()):
+                raise KernelError("per-head numbers of the attention are 32-bit, one per query head")
+        return SbFlex(_ptr(q), q.stride(0) if q is not None else 0, q.stride(1) if q is not None else 0, _ptr(k), _ptr(v),
+                      g.table.data_ptr(), _ptr(head_scale), _ptr(slopes), _ptr(sink), g.table_width, g.ring_pages, n_heads,
+                      g.request.num_kv_heads, g.request.head_dim, v_dim, v_row, int(window or 0), int(chunk or 0), float(scale))
+
+    def flex_attention(self, ctx, q, layer_cache, scale, v_dim, values_in_keys=False, sink=None, head_scale=None, slopes=None,
+                       chunk=None, window=None):
+        """Causal attention of the step's rows, q a view [rows, heads, key width] (last axis contiguous), over the
+        layer's cache -> [rows, heads * v_dim].  score = q.k * scale * head_scale[h] - slopes[h] * distance; ``chunk``
+        and ``window`` narrow what a row sees; ``sink`` [heads] adds exp(sink_h) to the softmax's denominator;
+        ``values_in_keys``: the values are the first v_dim columns of the key rows."""
+        rows, H, kd = q.shape
+        if q.stride(2) != 1 or kd != layer_cache.group.request.head_dim or q.dtype != layer_cache.k.dtype:
+            raise KernelError(f"flex_attention: q {tuple(q.shape)} {q.dtype} does not fit the layer's cache")
+        if H % layer_cache.group.request.num_kv_heads:
+            raise KernelError(f"{H} query heads cannot share {layer_cache.group.request.num_kv_heads} key/value heads evenly")
+        p = self._flex(layer_cache, q, H, scale, v_dim, values_in_keys, sink, head_scale, slopes, chunk, window)
+        out = torch.empty((rows, H * v_dim), dtype=q.dtype, device=q.device)
+        if v_dim > 512:
+            raise KernelError(f"attention takes values of up to 512 columns, not {v_dim}")
+        self._check(self.lib.sb_flex_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), self._stream()),
+                    "flex_attention_general")
+        return out
+
+    def kv_store(self, ctx, k, v, layer_cache, value_norm_eps=None):
+        """The step's keys [rows, kv_heads * key width] and values [rows, kv_heads * value width] (views of wider rows
+        will do) into the layer's cache; with ``value_norm_eps`` every head's value is divided by its root mean square."""
+        g = layer_cache.group
+        G = g.request.num_kv_heads
+        if (k.shape[1] != G * g.request.head_dim or v.shape[1] != G * g.v_dim or k.stride(1) != 1 or v.stride(1) != 1
+                or k.dtype != layer_cache.k.dtype or v.dtype != k.dtype):
+            raise KernelError("kv_store: keys or values do not fit the layer's cache")
+        p = self._flex(layer_cache)
+        self._check(self.lib.sb_kv_store(_code(k.dtype), _ptr(k), k.stride(0), _ptr(v), v.stride(0), self._batch(ctx), p,
+                                         int(value_norm_eps is not None), float(value_norm_eps or 0.0), _ptr(ctx.status),
+                                         self._stream()), "kv_store")
+
+    def rotate_pairs(self, ctx, src, dst, freqs, rot):
+        """dst = src [rows, heads, cols] (views, last axis contiguous) with the first ``rot`` columns of every head
+        turned in neighbouring pairs by the row's position times ``freqs`` (32-bit, [rot / 2])."""
+        rows, H, cols = src.shape
+        if tuple(dst.shape) != (rows, H, cols) or src.stride(2) != 1 or dst.stride(2) != 1 or src.dtype != dst.dtype:
+            raise KernelError("rotate_pairs: source and destination differ")
+        if freqs is None:
+            rot = 0
+        elif freqs.dtype != torch.float32 or freqs.numel() * 2 != rot:
+            raise KernelError("rotate_pairs: one 32-bit frequency per pair")
+        self._check(self.lib.sb_rotate_pairs(_code(src.dtype), _ptr(src), src.stride(0), src.stride(1), _ptr(dst), dst.stride(0),
+                                             dst.stride(1), self._batch(ctx), _ptr(freqs), H, cols, int(rot), self._stream()),
+                    "rotate_pairs")
+
+    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot):
+        """down [rows, q_rank + kv_rank + rot_dim] -> the normed query latent [rows, q_rank]; the normed key/value
+        latent and the rotated shared part go to the row's place in the layer's cache."""
+        if down.shape[1] != q_rank + kv_rank + rot_dim or not down.is_contiguous() or q_norm.dtype != kv_norm.dtype:
+            raise KernelError("latent_prepare: the down-projection has the wrong width")
+        if down.dtype == torch.float32 and q_norm.dtype != torch.float32:
+            raise KernelError("a float32 run needs float32 norm weights")
+        if freqs is None:
+            rot = 0
+        p = self._flex(layer_cache, values_in_keys=True)
+        cq = torch.empty((down.shape[0], q_rank), dtype=down.dtype, device=down.device)
+        self._check(self.lib.sb_latent_prepare(_code(down.dtype), _code(q_norm.dtype), _ptr(down), _ptr(cq), self._batch(ctx), p,
+                                               q_rank, kv_rank, rot_dim, _ptr(q_norm), _ptr(kv_norm), float(eps), _ptr(freqs),
+                                               int(rot), _ptr(ctx.status), self._stream()), "latent_prepare")
+        return cq
+
+    def token_shift(self, ctx, h, state, prev_offset, mu):
+        """[n, rows, width]: h + (h' - h) * mu[m] for every row of mu, h' the row before (for a sequence's first row of
+        the step: what its record in ``state`` [slots, floats] holds from ``prev_offset`` on)."""
+        rows, width = h.shape
+        if state.dtype != torch.float32 or mu.shape[1] != width or not h.is_contiguous() or not mu.is_contiguous():
+            raise KernelError("token_shift: a 32-bit state record and one blend vector per output")
+        out = torch.empty((mu.shape[0], rows, width), dtype=h.dtype, device=h.device)
+        self._check(self.lib.sb_token_shift(_code(h.dtype), _code(mu.dtype), _ptr(h), _ptr(state), state.stride(0), int(prev_offset),
+                                            _ptr(mu), mu.shape[0], self._batch(ctx), width, _ptr(out), self._stream()),
+                    "token_shift")
+        return out
+
+    def wkv_scan(self, ctx, r, k, v, g, decay_pre, w0, u, norm, eps, h, state, heads, dim, prev_offset):
+        """The recurrence over every sequence's rows, from and back into ``state``; returns the heads' outputs after the
+        unit norm, the scale and the gate [rows, heads * dim].  Also leaves each sequence's last row of h in its record."""
+        inner = heads * dim
+        if dim > 128:
+            raise KernelError(f"the recurrence takes heads of up to 128 channels, not {dim}")
+        for t in (r, k, v, g):
+            if tuple(t.shape) != (h.shape[0], inner) or not t.is_contiguous() or t.dtype != h.dtype:
+                raise KernelError("wkv_scan: r, k, v, g are contiguous [rows, heads * dim] in the run's dtype")
+        for t in (decay_pre, w0, u, norm):
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise KernelError("wkv_scan: decay, bonus and norm weights are 32-bit")
+        y = torch.empty((h.shape[0], inner), dtype=h.dtype, device=h.device)
+        self._check(self.lib.sb_wkv_scan(_code(h.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(g), _ptr(decay_pre), _ptr(w0), _ptr(u),
+                                         _ptr(norm), float(eps), _ptr(h), h.shape[1], _ptr(state), state.stride(0),
+                                         int(prev_offset), self._batch(ctx), heads, dim, _ptr(y), self._stream()), "wkv_scan")
+        return y
 
     # ---- sampling -----------------------------------------------------------------------
 

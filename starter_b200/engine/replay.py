@@ -37,8 +37,20 @@ def build_parser() -> argparse.ArgumentParser:
                    help="bfloat16: the kernels and precisions that serving uses; float32: everything in true 32-bit")
     p.add_argument("--out", required=True, help="folder that receives <step>.f32")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help=f"the most tokens live requests hold at any time, each rounded up to {PAGE}; sizes the cache")
+                   help="the most tokens live requests hold at any time; sizes the cache")
+    p.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                   help="the most requests that are live at any time (each may leave its last page partly empty)")
     return p
+
+
+MAX_LIVE_REQUESTS = 128
+
+
+def cache_room(max_tokens: int, max_requests: int):
+    """(tokens of cache, sequence slots) for a trace whose live requests hold ``max_tokens`` tokens at most: the cache
+    hands out whole pages, so every live request may waste up to one page less one token."""
+    slots = max(1, min(int(max_requests), int(max_tokens)))
+    return int(max_tokens) + slots * (PAGE - 1), slots
 
 
 def run(args, stdin=None, stdout=None) -> int:
@@ -46,7 +58,8 @@ def run(args, stdin=None, stdout=None) -> int:
     stdout = stdout or sys.stdout
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
-    session = Session(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    room, n_slots = cache_room(args.max_tokens, getattr(args, "max_requests", MAX_LIVE_REQUESTS))
+    session = Session(args.model, dtype=args.dtype, max_tokens=room, max_seqs=n_slots, max_seq_tokens=args.max_tokens)
     slots = {}
     for line in stdin:
         line = line.strip()
