@@ -111,6 +111,7 @@ class Ops:
             "sb_gemm_heads": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
                               c_int, c_int, c_void_p],
             "sb_flex_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_void_p],
+            "sb_flex_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
             "sb_kv_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, SbBatch, SbFlex, c_int, c_float, c_void_p, c_void_p],
             "sb_rotate_pairs": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, SbBatch, c_void_p,
                                 c_int, c_int, c_int, c_void_p],
@@ -128,6 +129,8 @@ class Ops:
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        lib.sb_flex_attention_mma_smem.argtypes = [c_int, c_int, c_int, c_int]
+        lib.sb_flex_attention_mma_smem.restype = c_longlong
         lib.sb_set_pdl.argtypes = [c_int]
         lib.sb_set_pdl.restype = None
         self._scratch = {}
@@ -148,6 +151,7 @@ class Ops:
         self.fuse_qk_balanced = os.environ.get("STARTER_B200_FUSE_QK_BALANCED", "0") != "0"
         self.prefetch_next_bytes = int(os.environ.get("STARTER_B200_PREFETCH_MAX", 24 << 20))
         self.prefill_tensor_memory = os.environ.get("STARTER_B200_PREFILL", "tc") != "mma"
+        self.flex_tensor_cores = os.environ.get("STARTER_B200_FLEX", "mma") != "general"   # "general": the warp-per-row kernel only
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -750,9 +754,48 @@ class Ops:
         out = torch.empty((rows, H * v_dim), dtype=q.dtype, device=q.device)
         if v_dim > 512:
             raise KernelError(f"attention takes values of up to 512 columns, not {v_dim}")
+        if self._flex_takes_mma(q, p, values_in_keys):
+            n_splits = self.flex_splits(ctx, p, layer_cache.group.table_width)
+            partial = None
+            if n_splits > 1:
+                key = ("flex_partial", q.device, rows, H, n_splits, v_dim)
+                partial = self._scratch.get(key)
+                if partial is None:
+                    partial = self._scratch[key] = torch.empty(rows * H * n_splits * (v_dim + 2), dtype=torch.float32, device=q.device)
+            self._check(self.lib.sb_flex_attention_mma(p, self._batch(ctx), _ptr(out), ctx.max_q_len, n_splits, _ptr(partial),
+                                                       int(values_in_keys), self._stream()), "flex_attention_mma")
+            if n_splits > 1:
+                self.launches += 1   # the merge of the splits
+            return out
         self._check(self.lib.sb_flex_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), self._stream()),
                     "flex_attention_general")
         return out
+
+    MAX_BLOCK_SHARED = 227 * 1024
+
+    def _flex_takes_mma(self, q, p: SbFlex, values_in_keys: bool) -> bool:
+        """The tensor-core kernel takes bfloat16, key widths that are multiples of 16, values of 64, 128, 256 or 512
+        columns, 1, 2, 4, 8 or a multiple of 16 query heads per key/value head, and rows it can fetch 16 bytes at a
+        time; the warp-per-row kernel serves everything else (and every 32-bit run)."""
+        if not self.flex_tensor_cores or q.dtype != torch.bfloat16:
+            return False
+        smem = self.lib.sb_flex_attention_mma_smem(p.k_dim, p.v_dim, p.n_heads // p.n_kv_heads, int(values_in_keys))
+        if smem < 0 or smem > self.MAX_BLOCK_SHARED:
+            return False
+        return q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.data_ptr() % 16 == 0 and p.v_row % 8 == 0
+
+    def flex_splits(self, ctx, p: SbFlex, max_pages: int) -> int:
+        """Blocks along the keys per (sequence, key/value head) in a step of one token per sequence: enough for two
+        blocks per SM, none with less than two pages.  A function of shapes only, so that a captured graph stays valid."""
+        if ctx.max_q_len != 1:
+            return 1
+        per_kv = p.n_heads // p.n_kv_heads
+        blocks = ctx.n_seqs * p.n_kv_heads * max(1, per_kv // 16)
+        reach = max_pages
+        for r in (p.window, p.chunk):
+            if r:
+                reach = min(reach, r // 64 + 2)
+        return max(1, min(-(-2 * self.sm_count() // blocks), reach // 2, 64))
 
     def kv_store(self, ctx, k, v, layer_cache, value_norm_eps=None):
         """The step's keys [rows, kv_heads * key width] and values [rows, kv_heads * value width] (views of wider rows

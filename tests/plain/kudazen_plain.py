@@ -214,3 +214,32 @@ def generate(cfg, tensors, prompts, max_new_tokens: int, mode: str = "float32"):
             seq.append(tok)
         outs.append(new)
     return outs
+
+
+def attend(q, k, v, scale, temp=None, slopes=None, chunk=None, sink=None, first_position=0):
+    """Dense attention of queries q [Tq, H, Kd] at positions first_position.. over keys k [T, G, Kd] and values
+    v [T, G, Vd] at positions 0..T-1 (T = first_position + Tq), every option of the two attention mixers at once:
+    score = q.k * scale * temp_h - slopes_h * (i - j); j visible when j <= i and, with ``chunk``, in i's block;
+    ``sink`` adds exp(sink_h) to the denominator."""
+    Tq, H, _ = q.shape
+    T, G, _ = k.shape
+    kk, vv = k.repeat_interleave(H // G, dim=1), v.repeat_interleave(H // G, dim=1)
+    i = torch.arange(first_position, first_position + Tq)[:, None]
+    j = torch.arange(T)[None, :]
+    scores = torch.einsum("ihd,jhd->hij", q, kk) * scale
+    if temp is not None:
+        scores = scores * temp.reshape(H, 1, 1)
+    if slopes is not None:
+        scores = scores - slopes.reshape(H, 1, 1) * (i - j).to(torch.float32)[None]
+    seen = j <= i
+    if chunk is not None:
+        seen = seen & ((i // chunk) == (j // chunk))
+    scores = scores.masked_fill(~seen[None], -math.inf)
+    top = scores.max(dim=-1, keepdim=True).values
+    if sink is not None:
+        top = torch.maximum(top, sink.reshape(H, 1, 1))
+    e = torch.exp(scores - top)
+    total = e.sum(dim=-1, keepdim=True)
+    if sink is not None:
+        total = total + torch.exp(sink.reshape(H, 1, 1) - top)
+    return torch.einsum("hij,jhv->ihv", e / total, vv)
