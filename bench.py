@@ -390,6 +390,206 @@ def run_check(args, raw, workload) -> int:
 
 # ---- the reference --------------------------------------------------------------------------------
 
+# ---- another model family beside the Qwen3 shape of equal size --------------------------------------
+
+def _kudazen_raw(width, ff, layers, latent, wkv, attention, vocab=32000):
+    """A Kudazen configuration of ``layers`` layers that cycle through the three mixers."""
+    kinds = [
+        {"type": "latent_attention", "mixer": dict(latent, scale=(latent["dim"] + latent["rot_dim"]) ** -0.5,
+                                                   rot={"base": 10000.0, "dims": latent["rot_dim"]})},
+        {"type": "wkv", "mixer": dict(wkv)},
+        {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5)},
+    ]
+    entries = [dict(kinds[i % 3], mlp={"kind": "dense", "ff": ff, "limit": 7.0}) for i in range(layers)]
+    return {"architecture": "Kudazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2}, "layers": entries}
+
+
+FAMILY_SIZES = {
+    # name: (Kudazen configuration, the Qwen3 configuration of the same width, feed-forward, layers and vocabulary)
+    "1024": (_kudazen_raw(1024, 4096, 6, dict(heads=8, dim=64, rot_dim=32, vdim=64, q_rank=384, kv_rank=256),
+                          dict(heads=16, dim=64, decay_rank=64), dict(heads=16, kv_heads=4, dim=64, vdim=64, mask={"size": 1024})),
+             dict(architectures=["Qwen3ForCausalLM"], hidden_size=1024, intermediate_size=4096, num_hidden_layers=6,
+                  num_attention_heads=16, num_key_value_heads=4, head_dim=64, vocab_size=32000, rms_norm_eps=1e-6,
+                  rope_theta=1000000.0, tie_word_embeddings=True)),
+    "2048": (_kudazen_raw(2048, 8192, 6, dict(heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512),
+                          dict(heads=32, dim=64, decay_rank=64), dict(heads=16, kv_heads=8, dim=128, vdim=128, mask={"size": 2048})),
+             dict(architectures=["Qwen3ForCausalLM"], hidden_size=2048, intermediate_size=8192, num_hidden_layers=6,
+                  num_attention_heads=16, num_key_value_heads=8, head_dim=128, vocab_size=32000, rms_norm_eps=1e-6,
+                  rope_theta=1000000.0, tie_word_embeddings=True)),
+}
+
+
+class TimedOps:
+    """The kernel call table with a pair of CUDA events around every call: per call name, the device time and what
+    the call must move or compute at least, from its arguments (the bound is the slower of the two)."""
+
+    def __init__(self, ops, torch, peaks):
+        self._ops, self._torch, self._peaks = ops, torch, peaks
+        self.records = []      # (name, start event, end event, bytes, flops)
+        self.ctx_tokens = 0    # tokens every sequence of the step holds (set by the caller: sizes the attention's work)
+
+    @staticmethod
+    def _nbytes(values):
+        total = 0
+        for v in values:
+            if hasattr(v, "element_size") and hasattr(v, "numel"):
+                total += v.numel() * v.element_size()
+            elif isinstance(v, (tuple, list)):
+                total += TimedOps._nbytes(v)
+        return total
+
+    def _cost(self, name, args, kwargs, out):
+        nbytes = self._nbytes(args) + self._nbytes(kwargs.values()) + self._nbytes([out])
+        flops = 0.0
+        if name in ("linear", "linear_swiglu"):
+            a, w = args[0], args[1]
+            flops = 2.0 * a.shape[0] * w.shape[0] * w.shape[1]
+        elif name == "linear_heads":
+            a, w = args[0], args[1]
+            flops = 2.0 * a.shape[0] * w.shape[0] * w.shape[1] * w.shape[2]
+            nbytes = w.numel() * 2 + 2 * a.shape[0] * w.shape[0] * (w.shape[1] + w.shape[2])
+        elif name in ("flex_attention", "attention", "qk_attention"):
+            ctx, q, cache = args[0], args[1], args[2]
+            req, group = cache.group.request, cache.group
+            v_dim = group.v_dim if group.v_dim else kwargs.get("v_dim", req.head_dim)
+            heads = q.shape[1] if name == "flex_attention" else args[3]
+            reach = self.ctx_tokens
+            for r in (kwargs.get("chunk"), kwargs.get("window"), req.window):
+                if r:
+                    reach = min(reach, r)
+            if ctx.max_q_len == 1:
+                pairs = float(ctx.n_rows) * reach
+                cache_bytes = ctx.n_seqs * reach * req.num_kv_heads * (req.head_dim + (group.v_dim or 0)) * 2
+            else:
+                t = ctx.n_rows / ctx.n_seqs
+                pairs = ctx.n_seqs * (t * (t + 1) / 2.0 if reach >= t else t * reach / 2.0)
+                cache_bytes = ctx.n_rows * req.num_kv_heads * (req.head_dim + (group.v_dim or 0)) * 2
+            flops = 2.0 * pairs * heads * (req.head_dim + v_dim)
+            nbytes = cache_bytes + 2 * self._nbytes([q]) if name != "qk_attention" else cache_bytes + self._nbytes([q])
+        elif name == "wkv_scan":
+            r, state, heads, dim = args[1], args[11], args[12], args[13]
+            flops = 6.0 * r.shape[0] * heads * dim * dim
+            nbytes = 2 * args[0].n_seqs * heads * dim * dim * 4 + 6 * r.numel() * 2
+        return nbytes, flops
+
+    def __getattr__(self, name):
+        attr = getattr(self._ops, name)
+        if not callable(attr) or name in ("prepare_matrix", "folds", "sm_count", "status_into", "set_dependent_launch",
+                                          "read_kernel_status", "kernel_status", "uneven_matters"):
+            return attr
+
+        def timed(*args, **kwargs):
+            t0 = self._torch.cuda.Event(enable_timing=True)
+            t1 = self._torch.cuda.Event(enable_timing=True)
+            t0.record()
+            out = attr(*args, **kwargs)
+            t1.record()
+            if out is not None or name not in ("qk_attention",):
+                self.records.append((name, t0, t1) + self._cost(name, args, kwargs, out))
+            return out
+        return timed
+
+    def table(self):
+        """{call name: {calls, us (all calls of one pass), bound_us, frac_of_bound}}, of the records since the last clear."""
+        self._torch.cuda.synchronize()
+        hbm, tflops = self._peaks["hbm_gbs"] * 1e9, self._peaks["bf16_tflops"] * 1e12
+        rows = {}
+        for name, t0, t1, nbytes, flops in self.records:
+            row = rows.setdefault(name, {"calls": 0, "us": 0.0, "bound_us": 0.0})
+            row["calls"] += 1
+            row["us"] += t0.elapsed_time(t1) * 1e3
+            row["bound_us"] += max(nbytes / hbm, flops / tflops) * 1e6
+        for row in rows.values():
+            row["frac_of_bound"] = round(row["bound_us"] / row["us"], 4) if row["us"] else None
+            row["us"], row["bound_us"] = round(row["us"], 1), round(row["bound_us"], 2)
+        return rows
+
+
+def _family_arm(torch, raw, peaks, prefill_tokens, batch, context, steps, warmup):
+    """Prefill and decode throughput of one configuration with random weights, and its kernels' times by call name
+    (one eager prefill pass and one eager decode step with events around every call)."""
+    from starter_b200.config import config_from_dict
+    from starter_b200.engine.session import Session
+    from starter_b200.engine.step import StepEntry
+    from starter_b200.sampling import SamplingParams
+    from starter_b200.weights import RandomSource
+    cfg = config_from_dict(raw)
+    source = RandomSource(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+    session = Session((cfg, source), dtype="bfloat16", max_tokens=max(batch * context, prefill_tokens) + 64 * batch, max_seqs=batch,
+                      max_seq_tokens=max(context, prefill_tokens), max_step_tokens=prefill_tokens, max_rows=max(prefill_tokens, 8192),
+                      device="cuda:0", verbose=False)
+    for group in session.cache.groups:     # a context of random keys, values and states stands in for real prompts
+        for name in ("k", "v", "data"):
+            t = getattr(group, name, None)
+            if t is not None:
+                t.normal_(0.0, 0.5)
+    out = {}
+    ms = time_prefill(session, [prefill_tokens], 5, torch)
+    out["prefill_tok_s"], out["prefill_ms"] = round(prefill_tokens * 1000.0 / ms, 1), round(ms, 3)
+    ms, _ = time_decode(session, SamplingParams(), [context - steps - warmup] * batch, steps, warmup, torch)
+    out["decode_tok_s"], out["decode_ms_per_step"] = round(batch * 1000.0 / ms, 1), round(ms, 4)
+    out["decode_launches"] = count_step_launches(session, SamplingParams(), batch, torch)
+    # per call name: swap the call table of the runtime (every part reads it there) for the timed one
+    timed = TimedOps(session.runtime.ops, torch, peaks)
+    parts = [p for p in session.model.parts()] + [getattr(p, "position", None) for p in session.model.parts()]
+    holders = [session.runtime] + [p for p in parts if p is not None and hasattr(p, "ops")]
+    saved = [h.ops for h in holders]
+    for h in holders:
+        h.ops = timed
+    try:
+        g = torch.Generator().manual_seed(3)
+        cache = session.cache
+        for label, n_seqs, rows, held in (("prefill", 1, prefill_tokens, 0), ("decode", batch, 1, context - 1)):
+            best = None
+            for _ in range(3):
+                slots = [cache.alloc() for _ in range(n_seqs)]
+                try:
+                    for sl in slots:
+                        cache.assume_length(sl, held)
+                    cache.flush()
+                    timed.records, timed.ctx_tokens = [], held + rows
+                    session.stepper.step([StepEntry(sl, torch.randint(0, session.vocab_size, (rows,), generator=g).tolist(), [rows - 1])
+                                          for sl in slots])
+                    table = timed.table()
+                finally:
+                    for sl in slots:
+                        cache.free(sl)
+                if best is None or sum(r["us"] for r in table.values()) < sum(r["us"] for r in best.values()):
+                    best = table
+            out[label + "_calls"] = best
+    finally:
+        for h, ops in zip(holders, saved):
+            h.ops = ops
+    return out
+
+
+def run_family(args) -> int:
+    """--family kudazen: the Kudazen design at a few sizes that resemble a real model's layers (random weights),
+    beside the Qwen3 decoder of the same width, feed-forward size, layer count and vocabulary.  One JSON line."""
+    import torch
+    peaks, peak_source = load_peaks()
+    torch.cuda.set_device(0)
+    sizes = [s for s in (args.sizes.split(",") if args.sizes else sorted(FAMILY_SIZES)) if s]
+    result = {"family": args.family, "beside": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights",
+              "prefill_tokens": PREFILL_TOKENS, "decode_batch": args.batch, "decode_context": args.context, "steps": args.steps,
+              "warmup": args.warmup, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")}, "peaks_from": peak_source,
+              "timing": "CUDA events; decode through the captured graph; *_calls: one eager pass with events around every call "
+                        "(a call's time includes its launch), bound = max(bytes / copy bandwidth, flops / bf16 burst)",
+              "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in sizes:
+            if name not in FAMILY_SIZES:
+                print(f"unknown size {name!r}; known: {', '.join(sorted(FAMILY_SIZES))}", file=sys.stderr)
+                return 1
+            ours, beside = FAMILY_SIZES[name]
+            result["sizes"][name] = {
+                "kudazen": _family_arm(torch, ours, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup),
+                "qwen3": _family_arm(torch, beside, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup)}
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
+
 def _unavailable(why: str) -> int:
     print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
     return 0
@@ -592,6 +792,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0)
     ap.add_argument("--skip-points", action="store_true", help="leave out the further decode points")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--family", default="", choices=["", "kudazen"],
+                    help="instead of the default workload: this model family at a few layer sizes, beside the Qwen3 shape of equal size")
+    ap.add_argument("--sizes", default="", help="with --family: sizes to run, with commas between them (default: all)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -610,6 +813,11 @@ def main() -> int:
         return 1
     if args.check:
         return run_check(args, raw, workload)
+    if args.family:
+        args.batch = args.batch if "--batch" in sys.argv else 8
+        args.context = args.context if "--context" in sys.argv else 2048
+        args.steps = args.steps if "--steps" in sys.argv else 64
+        return run_family(args)
     return run_ours(args, raw, workload)
 
 

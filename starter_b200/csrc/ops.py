@@ -706,6 +706,8 @@ class Ops:
 
     # ---- attention with options, latents, the linear recurrence --------------------------
 
+    HEADS_LIBRARY_MIN_ROWS = 64
+
     def linear_heads(self, a, w, out):
         """out[m, h, :] = a[m, h, :] times w[h] transposed, for views a [rows, heads, K] and out [rows, heads, N] whose
         last axis is contiguous (a head's columns inside wider rows) and w [heads, N, K]."""
@@ -714,6 +716,10 @@ class Ops:
         if (tuple(w.shape) != (H, N, K) or tuple(out.shape) != (rows, H, N) or a.stride(2) != 1 or out.stride(2) != 1
                 or not w.is_contiguous() or not (a.dtype == w.dtype == out.dtype)):
             raise KernelError(f"linear_heads: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if a.dtype == torch.bfloat16 and rows > self.HEADS_LIBRARY_MIN_ROWS and K % 8 == 0 and N % 8 == 0:
+            # many rows: the library's batched product on the tensor cores, as the plain products of a prompt
+            out.copy_(torch.bmm(a.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1))
+            return out
         self._check(self.lib.sb_gemm_heads(_code(a.dtype), _ptr(a), a.stride(0), a.stride(1), _ptr(w), _ptr(out), out.stride(0),
                                            out.stride(1), rows, N, K, H, self._stream()), "gemm_heads")
         return out

@@ -32,64 +32,124 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
     }
 }
 
-#define WKV_TB 16   // tokens whose r, k and decay are staged in shared memory at a time
+#define WKV_TB 32   // tokens whose r, k, v and decay are staged in shared memory at a time
+#define WKV_IG 8    // threads that share a group of value channels: each holds D / 8 key channels of those columns of the state
+#define WKV_CJ 1    // value channels (columns of the state) per thread
 
-// One block per (sequence, head); thread j owns value channel j: column j of the state, D floats in registers.
-template <class T, int DMAX>
-__global__ void __launch_bounds__(DMAX) wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v,
-                                                        const T* __restrict__ g, const float* __restrict__ decay_pre,
-                                                        const float* __restrict__ w0, const float* __restrict__ u,
-                                                        const float* __restrict__ norm_w, float eps, const T* __restrict__ h, int width,
-                                                        float* __restrict__ state, long long state_stride, int prev_offset,
-                                                        SbBatch batch, int H, int D, T* __restrict__ y) {
+// One block per (sequence, head), ceil(D / WKV_CJ) * 8 threads.  Thread (jg, ig) owns the state's entries S[i][j] for the
+// E = ceil(D / 8) key channels i = ig * E .. ig * E + E - 1 and the WKV_CJ value channels from j = WKV_CJ * jg on, in
+// registers.  The eight threads of a column group are neighbouring lanes and add their shares of out_t[j] with three
+// shuffles.  EXACT: D = 8 * EMAX, so no entry needs a bounds test and r, k and the decay are read 16 bytes at a time;
+// a thread's key channels are then dealt out four at a time ((e / 4) * 8 + ig) * 4 + e % 4, so that the eight lanes
+// of a group read 128 consecutive bytes (no bank conflict), and what a thread reads serves its four columns: measured
+// on a B200 the shared-memory pipe, not arithmetic, bounds this kernel (a warp per column group re-reads r, k, decay).  Every entry of the state is a recurrence
+// of its own, so the walk over a sequence's tokens costs a few dependent operations per token, whatever the head's size.
+template <class T, int EMAX, bool EXACT>
+__global__ void __launch_bounds__(EMAX * WKV_IG * WKV_IG / WKV_CJ)
+wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
+                const float* __restrict__ decay_pre, const float* __restrict__ w0, const float* __restrict__ u,
+                const float* __restrict__ norm_w, float eps, const T* __restrict__ h, int width, float* __restrict__ state,
+                long long state_stride, int prev_offset, SbBatch batch, int H, int D, T* __restrict__ y) {
     extern __shared__ float sm[];
     float* rs = sm;                  // [WKV_TB][D]
     float* ks = rs + WKV_TB * D;
     float* ws = ks + WKV_TB * D;
-    float* os = ws + WKV_TB * D;
-    float* us = os + WKV_TB * D;     // [D]
+    float* vs = ws + WKV_TB * D;
+    float* os = vs + WKV_TB * D;
+    float* gs = os + WKV_TB * D;     // silu(g)
+    float* us = gs + WKV_TB * D;     // [D]
     float* w0s = us + D;             // [D]
     __shared__ float rstd_s[WKV_TB];
-    const int s = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
-    const int lane = j & 31, warp = j >> 5, n_warps = DMAX / 32;
-    for (int i = j; i < D; i += DMAX) {   // weights: they do not depend on the kernel before this one
+    __shared__ float bonus_s[WKV_TB];   // sum_i r_i u_i k_i of each staged token: the current token's own share, per unit of v_j
+    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, n_threads = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, n_warps = n_threads >> 5;
+    const int j = (tid / WKV_IG) * WKV_CJ, ig = tid % WKV_IG;   // j: the first of this thread's four columns
+    const int E = (D + WKV_IG - 1) / WKV_IG, i0 = ig * E;
+    auto chan = [&](int e) { return EXACT ? ((e >> 2) * WKV_IG + ig) * 4 + (e & 3) : i0 + e; };   // key channel of entry e
+    for (int i = tid; i < D; i += n_threads) {   // weights: they do not depend on the kernel before this one
         us[i] = u[head * D + i];
         w0s[i] = w0[head * D + i];
     }
     pdl_wait();
     const int slot = batch.seq_slot[s], row0 = batch.cu_q[s], row1 = batch.cu_q[s + 1];
-    const int HD = H * D, col = head * D + j;
-    const bool own = j < D;
+    const int HD = H * D;
     float* Sg = state + (long long)slot * state_stride + (long long)head * D * D;
-    float S[DMAX];
+    float S[EMAX][WKV_CJ];
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) S[i] = (own && i < D) ? Sg[i * D + j] : 0.f;
-    const float nw = own ? norm_w[col] : 0.f;
+    for (int e = 0; e < EMAX; ++e)
+#pragma unroll
+        for (int c = 0; c < WKV_CJ; ++c) S[e][c] = (j + c < D && e < E && chan(e) < D) ? Sg[chan(e) * D + j + c] : 0.f;
     for (int t0 = row0; t0 < row1; t0 += WKV_TB) {
         const int nt = min(WKV_TB, row1 - t0);
         __syncthreads();
-        for (int e = j; e < nt * D; e += DMAX) {
+#pragma unroll 4
+        for (int e = tid; e < nt * D; e += n_threads) {   // unrolled: the loads of four turns are in flight together
             const long long at = (long long)(t0 + e / D) * HD + head * D + e % D;
+            const float gv = to_f<T>(g[at]);
             rs[e] = to_f<T>(r[at]);
             ks[e] = to_f<T>(k[at]);
+            vs[e] = to_f<T>(v[at]);
             ws[e] = expf(-expf(decay_pre[at] + w0s[e % D]));
+            gs[e] = gv / (1.0f + expf(-gv));
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vj = own ? to_f<T>(v[(long long)(t0 + tt) * HD + col]) : 0.f;
-            const float* rt = rs + tt * D;
-            const float* kt = ks + tt * D;
-            const float* wt = ws + tt * D;
-            float o = 0.f;
+        // out_t[j] = sum_i r_i S[i][j] + v_j * sum_i r_i u_i k_i: the second sum is the same for every column
+        for (int tt = warp; tt < nt; tt += n_warps) {
+            float c = 0.f;
+            for (int i = lane; i < D; i += 32) c = fmaf(rs[tt * D + i] * us[i], ks[tt * D + i], c);
+            c = warp_sum(c);
+            if (lane == 0) bonus_s[tt] = c;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int tt = 0; tt < nt; ++tt) {   // unrolled: a token's shuffles overlap the next tokens' products
+            float vj[WKV_CJ], o[WKV_CJ];
 #pragma unroll
-            for (int i = 0; i < DMAX; ++i) {
-                if (i < D) {
-                    const float kv = kt[i] * vj;
-                    o = fmaf(rt[i], fmaf(us[i], kv, S[i]), o);
-                    S[i] = fmaf(wt[i], S[i], kv);
+            for (int c = 0; c < WKV_CJ; ++c) {
+                vj[c] = (EXACT || j + c < D) ? vs[tt * D + j + c] : 0.f;
+                o[c] = 0.f;
+            }
+            const float* rt = rs + tt * D + i0;
+            const float* kt = ks + tt * D + i0;
+            const float* wt = ws + tt * D + i0;
+            if (EXACT) {   // 16-byte reads, the same address for the lanes of one key group
+#pragma unroll
+                for (int e = 0; e < EMAX; e += 4) {
+                    {
+                        const int at = tt * D + ((e >> 2) * WKV_IG + ig) * 4;
+                        const float4 r4 = *reinterpret_cast<const float4*>(rs + at);
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
+                        const float4 w4 = *reinterpret_cast<const float4*>(ws + at);
+                        const float rr[4] = {r4.x, r4.y, r4.z, r4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+#pragma unroll
+                            for (int c = 0; c < WKV_CJ; ++c) {
+                                o[c] = fmaf(rr[q], S[e + q][c], o[c]);
+                                S[e + q][c] = fmaf(ww[q], S[e + q][c], kk[q] * vj[c]);
+                            }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < EMAX; ++e) {
+                    if (e < E && i0 + e < D) {
+                        const float re = rt[e], ke = kt[e], we = wt[e];
+#pragma unroll
+                        for (int c = 0; c < WKV_CJ; ++c) {
+                            o[c] = fmaf(re, S[e][c], o[c]);
+                            S[e][c] = fmaf(we, S[e][c], ke * vj[c]);
+                        }
+                    }
                 }
             }
-            if (own) os[tt * D + j] = o;
+#pragma unroll
+            for (int c = 0; c < WKV_CJ; ++c) {
+                o[c] += __shfl_xor_sync(0xffffffffu, o[c], 1);
+                o[c] += __shfl_xor_sync(0xffffffffu, o[c], 2);
+                o[c] += __shfl_xor_sync(0xffffffffu, o[c], 4);
+                if (ig == 0 && (EXACT || j + c < D)) os[tt * D + j + c] = fmaf(vj[c], bonus_s[tt], o[c]);
+            }
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += n_warps) {   // the head's root mean square, a warp per token
@@ -99,23 +159,20 @@ __global__ void __launch_bounds__(DMAX) wkv_scan_kernel(const T* __restrict__ r,
             if (lane == 0) rstd_s[tt] = 1.0f / sqrtf(ss / (float)D + eps);
         }
         __syncthreads();
-        if (own) {
-            for (int tt = 0; tt < nt; ++tt) {
-                const long long at = (long long)(t0 + tt) * HD + col;
-                const float gv = to_f<T>(g[at]);
-                y[at] = from_f<T>(os[tt * D + j] * rstd_s[tt] * nw * (gv / (1.0f + expf(-gv))));
-            }
+        for (int e = tid; e < nt * D; e += n_threads) {
+            const int tt = e / D, c = e % D;
+            y[(long long)(t0 + tt) * HD + head * D + c] = from_f<T>(os[e] * rstd_s[tt] * norm_w[head * D + c] * gs[e]);
         }
     }
-    if (own) {
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < D) Sg[i * D + j] = S[i];
-    }
+    for (int e = 0; e < EMAX; ++e)
+#pragma unroll
+        for (int c = 0; c < WKV_CJ; ++c)
+            if (j + c < D && e < E && chan(e) < D) Sg[chan(e) * D + j + c] = S[e][c];
     if (head == 0 && row1 > row0) {   // the last token's input: what the next step's first row blends with
         float* rec = state + (long long)slot * state_stride + prev_offset;
         const T* last = h + (long long)(row1 - 1) * width;
-        for (int c = j; c < width; c += DMAX) rec[c] = to_f<T>(last[c]);
+        for (int c = tid; c < width; c += n_threads) rec[c] = to_f<T>(last[c]);
     }
 }
 
@@ -143,20 +200,31 @@ int sb_wkv_scan(int dtype, const void* r, const void* k, const void* v, const vo
     if (batch.n_seqs <= 0 || batch.n_rows <= 0) return 0;
     if (D < 1 || D > 128 || H > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid(batch.n_seqs, H);
-    const size_t smem = (size_t)(4 * WKV_TB + 2) * D * sizeof(float);
+    const size_t smem = (size_t)(6 * WKV_TB + 2) * D * sizeof(float);
+    const int threads = ((D + WKV_CJ - 1) / WKV_CJ * WKV_IG + 31) / 32 * 32;
     typedef __nv_bfloat16 bf;
-#define SB_WKV(T, DMAX)                                                                                                      \
-    sb_launch(wkv_scan_kernel<T, DMAX>, grid, DMAX, smem, stream, (const T*)r, (const T*)k, (const T*)v, (const T*)g, decay_pre, w0, u, \
-              norm_w, eps, (const T*)h, width, state, state_stride, prev_offset, batch, H, D, (T*)y)
-    if (dtype == SB_F32) {
-        if (D <= 32) SB_WKV(float, 32);
-        else if (D <= 64) SB_WKV(float, 64);
-        else SB_WKV(float, 128);
-    } else {
-        if (D <= 32) SB_WKV(bf, 32);
-        else if (D <= 64) SB_WKV(bf, 64);
-        else SB_WKV(bf, 128);
-    }
+#define SB_WKV(T, EMAX, EXACT)                                                                                                \
+    do {                                                                                                                      \
+        if (smem > 48 * 1024) {                                                                                               \
+            const cudaError_t err = cudaFuncSetAttribute(wkv_scan_kernel<T, EMAX, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                         (int)smem);                                                          \
+            if (err != cudaSuccess) return (int)err;                                                                          \
+        }                                                                                                                     \
+        sb_launch(wkv_scan_kernel<T, EMAX, EXACT>, grid, threads, smem, stream, (const T*)r, (const T*)k, (const T*)v, (const T*)g, \
+                  decay_pre, w0, u, norm_w, eps, (const T*)h, width, state, state_stride, prev_offset, batch, H, D, (T*)y);    \
+    } while (0)
+#define SB_WKV_SIZES(T)                              \
+    do {                                             \
+        if (D == 32) SB_WKV(T, 4, true);             \
+        else if (D == 64) SB_WKV(T, 8, true);        \
+        else if (D == 128) SB_WKV(T, 16, true);      \
+        else if (D <= 32) SB_WKV(T, 4, false);       \
+        else if (D <= 64) SB_WKV(T, 8, false);       \
+        else SB_WKV(T, 16, false);                   \
+    } while (0)
+    if (dtype == SB_F32) SB_WKV_SIZES(float);
+    else SB_WKV_SIZES(bf);
+#undef SB_WKV_SIZES
 #undef SB_WKV
     SB_LAUNCH_CHECK();
 }
