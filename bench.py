@@ -485,7 +485,10 @@ class TimedOps:
             out = attr(*args, **kwargs)
             t1.record()
             if out is not None or name not in ("qk_attention",):
-                self.records.append((name, t0, t1) + self._cost(name, args, kwargs, out))
+                label = name
+                if name == "flex_attention":   # the two users of this call apart: values inside the key rows (latent) or pages of their own
+                    label += "[latent]" if kwargs.get("values_in_keys") else "[chunked]"
+                self.records.append((label, t0, t1) + self._cost(name, args, kwargs, out))
             return out
         return timed
 

@@ -112,6 +112,7 @@ class Ops:
                               c_int, c_int, c_void_p],
             "sb_flex_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_void_p],
             "sb_flex_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+            "sb_flex_attention_rows64": [SbFlex, SbBatch, c_void_p, c_int, c_int, c_void_p],
             "sb_kv_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, SbBatch, SbFlex, c_int, c_float, c_void_p, c_void_p],
             "sb_rotate_pairs": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, SbBatch, c_void_p,
                                 c_int, c_int, c_int, c_void_p],
@@ -129,8 +130,9 @@ class Ops:
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
-        lib.sb_flex_attention_mma_smem.argtypes = [c_int, c_int, c_int, c_int]
-        lib.sb_flex_attention_mma_smem.restype = c_longlong
+        for fn in (lib.sb_flex_attention_mma_smem, lib.sb_flex_attention_rows64_smem):
+            fn.argtypes = [c_int, c_int, c_int, c_int]
+            fn.restype = c_longlong
         lib.sb_set_pdl.argtypes = [c_int]
         lib.sb_set_pdl.restype = None
         self._scratch = {}
@@ -760,6 +762,10 @@ class Ops:
         out = torch.empty((rows, H * v_dim), dtype=q.dtype, device=q.device)
         if v_dim > 512:
             raise KernelError(f"attention takes values of up to 512 columns, not {v_dim}")
+        if self._flex_takes_rows64(ctx, q, p, values_in_keys):
+            self._check(self.lib.sb_flex_attention_rows64(p, self._batch(ctx), _ptr(out), ctx.max_q_len, int(values_in_keys),
+                                                          self._stream()), "flex_attention_rows64")
+            return out
         if self._flex_takes_mma(q, p, values_in_keys):
             n_splits = self.flex_splits(ctx, p, layer_cache.group.table_width)
             partial = None
@@ -786,6 +792,22 @@ class Ops:
         if not self.flex_tensor_cores or q.dtype != torch.bfloat16:
             return False
         smem = self.lib.sb_flex_attention_mma_smem(p.k_dim, p.v_dim, p.n_heads // p.n_kv_heads, int(values_in_keys))
+        if smem < 0 or smem > self.MAX_BLOCK_SHARED:
+            return False
+        return q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.data_ptr() % 16 == 0 and p.v_row % 8 == 0
+
+    FLEX_PROMPT_MIN_ROWS = 32
+
+    def _flex_takes_rows64(self, ctx, q, p: SbFlex, values_in_keys: bool) -> bool:
+        """The kernel for prompts (64 rows per block, a warp per 16 rows, no meeting of warps inside a page) takes steps
+        whose sequences bring at least 32 rows of scores per key/value head, values of 64 or 128 columns and a number of
+        heads per key/value head that divides 64; the rest of what the tensor-core path takes goes to the 16-row kernel."""
+        if not self.flex_tensor_cores or q.dtype != torch.bfloat16:
+            return False
+        per_kv = p.n_heads // p.n_kv_heads
+        if ctx.max_q_len * per_kv < self.FLEX_PROMPT_MIN_ROWS:
+            return False
+        smem = self.lib.sb_flex_attention_rows64_smem(p.k_dim, p.v_dim, per_kv, int(values_in_keys))
         if smem < 0 or smem > self.MAX_BLOCK_SHARED:
             return False
         return q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.data_ptr() % 16 == 0 and p.v_row % 8 == 0

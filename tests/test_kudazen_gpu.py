@@ -262,6 +262,28 @@ def test_far_key_and_sink_through_the_latent_cache(mode, decode, H, Kd, Vd):
     assert float(want[-1].reshape(H, Vd)[2, :4].abs().max()) < 0.1 * 4   # a sink of 20 against a score of 14.4 takes nearly all the weight
 
 
+def test_both_tensor_core_kernels_serve_prompts(monkeypatch):
+    """The same prompt through the kernel for prompts (64 rows per block) and, with that one switched off, through the
+    16-row kernel: both within rounding of the plain formula, for the latent cache and for chunked keys with a penalty."""
+    from starter_b200.cache import KVRequest
+    rt = runtime("bfloat16")
+    T, H, G, D, V = 300, 8, 2, 64, 128
+    k, v, q = rand((T, G, D), 1, 0.5), rand((T, G, V), 2, 0.5), rand((T, H, D), 3, 0.5)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)])
+    temp = rand((H,), 4, 0.3, 1.0)
+    want = plain.attend(q, k, v, D ** -0.5, temp, slopes, 96).reshape(T, H * V)
+    kl, ql = rand((T, 1, 144), 5, 0.4), rand((T, 16, 144), 6, 0.4)
+    sink = rand((16,), 7, 1.0)
+    want_latent = plain.attend(ql, kl, kl[:, :, :128], 0.1, sink=sink).reshape(T, 16 * 128)
+    for rows in (32, 1 << 30):
+        monkeypatch.setattr(rt.ops, "FLEX_PROMPT_MIN_ROWS", rows)
+        got = fill_and_attend(rt, KVRequest(G, D, window=96, v_dim=V), k, v, q, 0, scale=D ** -0.5, v_dim=V, head_scale=temp.cuda(),
+                              slopes=slopes.cuda(), chunk=96)
+        close(got, want, "bfloat16", f"chunked, prompt kernel from {rows} rows")
+        got = fill_and_attend(rt, KVRequest(1, 144, v_dim=0), kl, None, ql, 0, scale=0.1, v_dim=128, values_in_keys=True, sink=sink.cuda())
+        close(got, want_latent, "bfloat16", f"latent, prompt kernel from {rows} rows")
+
+
 # ---- whole models ------------------------------------------------------------------------------------------
 
 @pytest.fixture(scope="module")
