@@ -12,8 +12,8 @@ optionally ``weights_of``: the index of the layer whose tensors this one runs wi
 own)}.  Tensors: ``embed``, ``final.norm``, and per layer that owns weights ``l<i>.norm1``, ``l<i>.mix.*``,
 ``l<i>.mlp.{gate,up,down}``.
 
-Constants the design fixes: the penalty's slopes 2**(-8 (h + 1) / heads), the feed-forward's sigmoid factor 1.702,
-the rotation over all of the rotated part.
+Constants the design fixes: the penalty's slopes 2**(-8 (h + 1) / heads) and the feed-forward's sigmoid factor 1.702.
+The rotation covers the first ``rot.dims`` columns of the rotated part (all of it in the models seen so far).
 """
 
 from __future__ import annotations
@@ -82,9 +82,10 @@ class KudazenConfig(ModelConfig):
                     _count(f"layers[{i}].mixer.{key}", m[key])
             if kind == "latent_attention":
                 _need(f"layers[{i}].mixer.rot", m["rot"], ("base", "dims"))
-                if m["rot"]["dims"] != m["rot_dim"] or m["rot_dim"] % 2:
-                    raise ConfigError(f"config.json: layers[{i}] rotates {m['rot']['dims']} of {m['rot_dim']} columns; "
-                                      "the rotation covers all of an even rotated part")
+                dims = m["rot"]["dims"]
+                if isinstance(dims, bool) or not isinstance(dims, int) or dims < 2 or dims % 2 or dims > m["rot_dim"]:
+                    raise ConfigError(f"config.json: layers[{i}] rotates {dims!r} of {m['rot_dim']} columns; the rotation "
+                                      "covers an even number of the rotated part's first columns")
             if kind == "attention":
                 _need(f"layers[{i}].mixer.mask", m["mask"], ("size",))
                 _count(f"layers[{i}].mixer.mask.size", m["mask"]["size"])

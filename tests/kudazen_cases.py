@@ -17,10 +17,10 @@ from starter_b200.config import config_from_dict
 from starter_b200.weights import write_model_folder
 
 
-def _latent(heads, dim, rot, vdim, q_rank, kv_rank, base=10000.0):
+def _latent(heads, dim, rot, vdim, q_rank, kv_rank, base=10000.0, dims=None):
     return {"type": "latent_attention",
             "mixer": {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
-                      "scale": (dim + rot) ** -0.5, "rot": {"base": base, "dims": rot}}}
+                      "scale": (dim + rot) ** -0.5, "rot": {"base": base, "dims": dims or rot}}}
 
 
 def _wkv(heads, dim, rank):
@@ -52,7 +52,7 @@ CASES = {
     # every mixer, two of them run twice on shared weights, one layer without feed-forward, three norm groups
     "A": _model(211, 96, 3, 1e-5, [_with(_A_LATENT, ff=72), _with(_A_WKV, ff=136, limit=1.0), _with(_A_ATT, ff=80),
                                    _with(_A_WKV, ff=136, limit=1.0, weights_of=1), _with(_A_ATT, ff=80, weights_of=2),
-                                   _with(_latent(2, 16, 8, 16, 24, 32))]),
+                                   _with(_latent(2, 16, 8, 16, 24, 32, dims=4))]),   # half of the rotated part turns
     # sizes the tensor-core kernels take (head sizes 32 and 64, chunk = one page), one norm group, another layer order
     "B": _model(300, 128, 1, 1e-6, [_with(_B_ATT, ff=200), _with(_B_LATENT, ff=200), _with(_B_WKV, ff=200),
                                     _with(_B_LATENT, ff=200, weights_of=1), _with(_B_ATT, ff=200, weights_of=0)]),

@@ -58,7 +58,8 @@ def test_decay_rank_comes_from_the_tensor_shape(folders, tmp_path):
     (lambda r: r["layers"][2]["mixer"].update(kv_heads=4), "evenly"),
     (lambda r: r["norm"].update(groups=5), "groups"),
     (lambda r: r["layers"][0]["mlp"].update(kind="experts"), "dense"),
-    (lambda r: r["layers"][0]["mixer"]["rot"].update(dims=4), "rotat"),
+    (lambda r: r["layers"][0]["mixer"]["rot"].update(dims=10), "rotat"),
+    (lambda r: r["layers"][0]["mixer"]["rot"].update(dims=3), "rotat"),
 ])
 def test_bad_configurations_are_refused(change, what):
     raw = copy.deepcopy(cases.CASES["A"])
