@@ -487,7 +487,8 @@ class TimedOps:
             if out is not None or name not in ("qk_attention",):
                 label = name
                 if name == "flex_attention":   # the two users of this call apart: values inside the key rows (latent) or pages of their own
-                    label += "[latent]" if kwargs.get("values_in_keys") else "[chunked]"
+                    label += ("[latent]" if kwargs.get("values_in_keys") else
+                              "[latent, narrow form]" if kwargs.get("sink") is not None else "[chunked]")
                 self.records.append((label, t0, t1) + self._cost(name, args, kwargs, out))
             return out
         return timed

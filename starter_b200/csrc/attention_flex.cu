@@ -173,17 +173,18 @@ __global__ void rotate_pairs_kernel(const T* __restrict__ src, long long s_row, 
 
 // One block per row of down = [query latent (q_rank) | key/value latent (kv_rank) | shared rotated part (rot_dim)]:
 // the query latent normed into cq, the key/value latent normed and the shared part rotated into the row's one
-// cache row [kv_rank + rot_dim].
+// cache row [kv_rank + rot_dim]; the same row also into row_out [rows, kv_rank + rot_dim] when that is given.
 template <class T, class W>
 __global__ void latent_prepare_kernel(const T* __restrict__ down, T* __restrict__ cq, SbBatch batch, SbFlex p, int q_rank, int kv_rank,
                                       int rot_dim, const W* __restrict__ q_norm, const W* __restrict__ kv_norm, float eps,
-                                      const float* __restrict__ freqs, int rot, int* status) {
+                                      const float* __restrict__ freqs, int rot, int* status, T* __restrict__ row_out) {
     __shared__ float red[33];
     pdl_wait();
     const int row = blockIdx.x;
     int slot, pos;
     row_place(batch, row, slot, pos);
     const T* dr = down + (long long)row * (q_rank + kv_rank + rot_dim);
+    T* ro = row_out != nullptr ? row_out + (long long)row * (kv_rank + rot_dim) : nullptr;
     float ss = 0.f;
     for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
         const float x = to_f<T>(dr[c]);
@@ -206,8 +207,11 @@ __global__ void latent_prepare_kernel(const T* __restrict__ down, T* __restrict_
     }
     rstd = 1.0f / sqrtf(ss / (float)kv_rank + eps);
     T* kd = (T*)p.k + tok * p.k_dim;
-    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x)
-        kd[c] = from_f<T>(__fmul_rn(__fmul_rn(to_f<T>(dr[q_rank + c]), rstd), to_f<W>(kv_norm[c])));
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        const T val = from_f<T>(__fmul_rn(__fmul_rn(to_f<T>(dr[q_rank + c]), rstd), to_f<W>(kv_norm[c])));
+        kd[c] = val;
+        if (ro != nullptr) ro[c] = val;
+    }
     const T* sr = dr + q_rank + kv_rank;
     const int half = rot / 2;
     for (int c = threadIdx.x; c < half + (rot_dim - rot); c += blockDim.x) {
@@ -215,10 +219,16 @@ __global__ void latent_prepare_kernel(const T* __restrict__ down, T* __restrict_
             float sn, cs;
             sincosf((float)pos * freqs[c], &sn, &cs);
             const float a = to_f<T>(sr[2 * c]), b = to_f<T>(sr[2 * c + 1]);
-            kd[kv_rank + 2 * c] = from_f<T>(a * cs - b * sn);
-            kd[kv_rank + 2 * c + 1] = from_f<T>(b * cs + a * sn);
+            const T x = from_f<T>(a * cs - b * sn), y = from_f<T>(b * cs + a * sn);
+            kd[kv_rank + 2 * c] = x;
+            kd[kv_rank + 2 * c + 1] = y;
+            if (ro != nullptr) {
+                ro[kv_rank + 2 * c] = x;
+                ro[kv_rank + 2 * c + 1] = y;
+            }
         } else {
             kd[kv_rank + rot + c - half] = sr[rot + c - half];
+            if (ro != nullptr) ro[kv_rank + rot + c - half] = sr[rot + c - half];
         }
     }
 }
@@ -265,14 +275,14 @@ int sb_rotate_pairs(int dtype, const void* src, long long s_row, long long s_hea
 }
 
 int sb_latent_prepare(int dtype, int w_dtype, const void* down, void* cq, SbBatch batch, SbFlex p, int q_rank, int kv_rank, int rot_dim,
-                      const void* q_norm, const void* kv_norm, float eps, const float* freqs, int rot, int* status,
+                      const void* q_norm, const void* kv_norm, float eps, const float* freqs, int rot, int* status, void* row_out,
                       cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (rot < 0 || rot > rot_dim || rot % 2 || p.k_dim != kv_rank + rot_dim) return (int)cudaErrorInvalidValue;
     typedef __nv_bfloat16 bf;
 #define SB_LP(T, W)                                                                                                          \
     sb_launch(latent_prepare_kernel<T, W>, batch.n_rows, 128, 0, stream, (const T*)down, (T*)cq, batch, p, q_rank, kv_rank, rot_dim, \
-              (const W*)q_norm, (const W*)kv_norm, eps, freqs, rot, status)
+              (const W*)q_norm, (const W*)kv_norm, eps, freqs, rot, status, (T*)row_out)
     if (dtype == SB_F32 && w_dtype == SB_F32) SB_LP(float, float);
     else if (dtype == SB_BF16 && w_dtype == SB_BF16) SB_LP(bf, bf);
     else if (dtype == SB_BF16 && w_dtype == SB_F32) SB_LP(bf, float);

@@ -117,7 +117,7 @@ class Ops:
             "sb_rotate_pairs": [c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, SbBatch, c_void_p,
                                 c_int, c_int, c_int, c_void_p],
             "sb_latent_prepare": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbFlex, c_int, c_int, c_int, c_void_p, c_void_p,
-                                  c_float, c_void_p, c_int, c_void_p, c_void_p],
+                                  c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
             "sb_token_shift": [c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, SbBatch, c_int, c_void_p,
                                c_void_p],
             "sb_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
@@ -852,9 +852,10 @@ class Ops:
                                              dst.stride(1), self._batch(ctx), _ptr(freqs), H, cols, int(rot), self._stream()),
                     "rotate_pairs")
 
-    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot):
+    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot, rows_too=False):
         """down [rows, q_rank + kv_rank + rot_dim] -> the normed query latent [rows, q_rank]; the normed key/value
-        latent and the rotated shared part go to the row's place in the layer's cache."""
+        latent and the rotated shared part go to the row's place in the layer's cache.  ``rows_too``: what went to the
+        cache is returned as well, (cq, [rows, kv_rank + rot_dim])."""
         if down.shape[1] != q_rank + kv_rank + rot_dim or not down.is_contiguous() or q_norm.dtype != kv_norm.dtype:
             raise KernelError("latent_prepare: the down-projection has the wrong width")
         if down.dtype == torch.float32 and q_norm.dtype != torch.float32:
@@ -863,10 +864,11 @@ class Ops:
             rot = 0
         p = self._flex(layer_cache, values_in_keys=True)
         cq = torch.empty((down.shape[0], q_rank), dtype=down.dtype, device=down.device)
+        kept = torch.empty((down.shape[0], kv_rank + rot_dim), dtype=down.dtype, device=down.device) if rows_too else None
         self._check(self.lib.sb_latent_prepare(_code(down.dtype), _code(q_norm.dtype), _ptr(down), _ptr(cq), self._batch(ctx), p,
                                                q_rank, kv_rank, rot_dim, _ptr(q_norm), _ptr(kv_norm), float(eps), _ptr(freqs),
-                                               int(rot), _ptr(ctx.status), self._stream()), "latent_prepare")
-        return cq
+                                               int(rot), _ptr(ctx.status), _ptr(kept), self._stream()), "latent_prepare")
+        return (cq, kept) if rows_too else cq
 
     def token_shift(self, ctx, h, state, prev_offset, mu):
         """[n, rows, width]: h + (h' - h) * mu[m] for every row of mu, h' the row before (for a sequence's first row of

@@ -75,7 +75,7 @@ class EmulatedOps:
         _, pos = self._positions(ctx)
         dst.copy_(self._turn(src.float(), pos, freqs, rot).to(dst.dtype))
 
-    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot):
+    def latent_prepare(self, ctx, down, layer_cache, q_rank, kv_rank, rot_dim, q_norm, kv_norm, eps, freqs, rot, rows_too=False):
         dt = down.dtype
         slots, pos = self._positions(ctx)
         d = down.float()
@@ -90,10 +90,11 @@ class EmulatedOps:
         if bool((page < 0).any()):
             ctx.status |= 2
         ok = page >= 0
-        layer_cache.k[page[ok], 0, off[ok]] = torch.cat([latent, shared], dim=-1)[ok].to(dt)
-        return cq
+        kept = torch.cat([latent, shared], dim=-1).to(dt)
+        layer_cache.k[page[ok], 0, off[ok]] = kept[ok]
+        return (cq, kept) if rows_too else cq
 
-    def kv_store(self, ctx, k, v, layer_cache, value_norm_eps):
+    def kv_store(self, ctx, k, v, layer_cache, value_norm_eps=None):
         group = layer_cache.group
         G, D, V = group.request.num_kv_heads, group.request.head_dim, group.v_dim
         slots, pos = self._positions(ctx)
