@@ -41,6 +41,15 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
                                    SbSkinnyNorm{nullptr, 0.f, nullptr, 0}, stats_out, partial, counters, stream);
 }
 
+// The same for a fused [gate; up] matrix with the clamped activation in the epilogue:
+// g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+int sb_gemm_skinny_gated(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split, int tiled,
+                         int warps, float alpha, float limit, float* partial, int* counters, cudaStream_t stream) {
+    if (!(limit > 0.f)) return (int)cudaErrorInvalidValue;
+    return skinny_launch<false, 4>(A, W, C, M, n_out, K, n_splits, k_per_split, 1, 0, tiled, warps, 0,
+                                   SbSkinnyNorm{nullptr, 0.f, nullptr, 0, alpha, limit}, nullptr, partial, counters, stream);
+}
+
 // The tile-major copy of a row-major matrix for the kernel above.  src [halves * rows, K] bfloat16 row-major; dst
 // holds halves * ceil(rows / 16) * ceil(K / 128) tiles of 16 x 128 (sb_tile_matrix_elements of them in all).
 long long sb_tile_matrix_elements(int rows, int K, int halves) {

@@ -63,6 +63,16 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
     return s * ub;
 }
 
+// gate and up as they read back from bfloat16 (what a product followed by an activation kernel would see), clamped.
+__device__ __forceinline__ float gated_act(float g, float u, float alpha, float limit) {
+    if (limit > 0.f) {
+        const float gb = fminf(__bfloat162float(__float2bfloat16_rn(g)), limit);
+        const float ub = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(u)), -limit), limit);
+        return gb / (1.0f + expf(-alpha * gb)) * (ub + 1.0f);
+    }
+    return silu_mul_bf16(g, u);
+}
+
 // NT: activation tiles of 8 rows (M <= 8 * NT).  GATE_UP: W is [2 * n_out, K], gate rows first; the first half of
 // the warps takes the gate rows of the block, the second half the matching up rows, and the output is swiglu(gate, up).
 // TILED: W is the tile-major copy that sb_tile_matrix makes: [row tile of 16][turn of 128 columns][16 rows][128
@@ -77,6 +87,10 @@ struct SbSkinnyNorm {
     float eps;
     const float* stats;
     int n_stats;
+    // what the GATE_UP epilogue computes: act_limit > 0 selects g' * sigmoid(act_alpha * g') * (u' + 1) with g' = min(g, limit)
+    // and u' = clamp(u, -limit, limit); 0 (what an initialiser that stops earlier leaves) the plain silu(g) * u
+    float act_alpha;
+    float act_limit;
 };
 
 // Stores one output and returns what C now holds there.
@@ -286,7 +300,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                     v += *cluster.map_shared_rank(&red[0][r][m], c);
                     if (GATE_UP) v2 += *cluster.map_shared_rank(&red[WPG][r][m], c);
                 }
-                if (GATE_UP) v = silu_mul_bf16(v, v2);
+                if (GATE_UP) v = gated_act(v, v2, norm.act_alpha, norm.act_limit);
                 stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
             }
             if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);
@@ -320,7 +334,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         float stored = 0.f;
         if (m < M && n0 + r < n_out) {
             float v = red[0][r][m];
-            if (GATE_UP) v = silu_mul_bf16(v, red[WPG][r][m]);
+            if (GATE_UP) v = gated_act(v, red[WPG][r][m], norm.act_alpha, norm.act_limit);
             stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
         }
         if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);

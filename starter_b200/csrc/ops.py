@@ -88,6 +88,8 @@ class Ops:
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
             "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+            "sb_gemm_skinny_gated": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                     c_void_p, c_void_p, c_void_p],
             "sb_gemm_skinny_normed": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_tile_matrix": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -402,7 +404,7 @@ class Ops:
     def _can_fold(self, rows: int, dtype, K: int) -> bool:
         return dtype == torch.bfloat16 and rows <= min(self.SKINNY_MAX_ROWS, 16) and K % 8 == 0
 
-    def _skinny(self, a, w, n_out, gate_up, out_float32, norm=None, add_to=None):
+    def _skinny(self, a, w, n_out, gate_up, out_float32, norm=None, add_to=None, act=None):
         """The weight-streaming product for a handful of rows (see gemm_skinny.cuh).
 
         norm: (weight, eps) or (weight, eps, stats) of an RMSNorm to take of a's rows first; stats is what the product
@@ -439,7 +441,13 @@ class Ops:
         src = copy[0] if copy is not None else w
         tail = (M, n_out, K, n_splits, k_per_split, int(gate_up), int(out_float32), int(copy is not None), warps,
                 int(add_to is not None), _ptr(stats_out), _ptr(buf[0]), _ptr(buf[1]), self._stream())
-        if norm is None:
+        if act is not None:   # (alpha, limit): the clamped activation in the epilogue of a [gate; up] product
+            if not gate_up or norm is not None or add_to is not None or out_float32:
+                raise KernelError("the clamped activation sits in the epilogue of a plain [gate; up] product")
+            self._check(self.lib.sb_gemm_skinny_gated(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split,
+                                                      int(copy is not None), warps, float(act[0]), float(act[1]), _ptr(buf[0]),
+                                                      _ptr(buf[1]), self._stream()), "gemm_skinny_gated")
+        elif norm is None:
             self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(src), _ptr(out), *tail), "gemm_skinny")
         else:
             gamma, eps, stats = norm if len(norm) == 3 else (*norm, None)
@@ -497,6 +505,14 @@ class Ops:
             if M <= self.SKINNY_MAX_ROWS:
                 return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
         return self.swiglu(self.linear(h, w_gate_up))
+
+    def linear_gated_clamp(self, h, w_gate_up, alpha, limit):
+        """gated_clamp(h @ w_gate_up^T) for a fused [gate; up] matrix: [M, K] -> [M, rows / 2].  For the few rows of a decode
+        step the activation sits in the product's epilogue, as SwiGLU does in ``linear_swiglu``."""
+        M, K = h.shape
+        if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0 and M <= self.SKINNY_MAX_ROWS:
+            return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False, act=(alpha, limit))
+        return self.gated_clamp(self.linear(h, w_gate_up), alpha, limit)
 
     # ---- attention ----------------------------------------------------------------------
 

@@ -44,8 +44,7 @@ class GatedMLP:
         """h is the normed input; with ``norm`` it is the residual itself and the norm is taken inside the first
         product; with ``residual`` the result is added to that tensor instead of being returned on its own."""
         if self.activation == "clamped_swish":
-            act = self.ops.gated_clamp(self.ops.linear(h, self.w_gate_up), self.alpha, self.limit)
-            return self.ops.linear(act, self.w_down)
+            return self.ops.linear(self.ops.linear_gated_clamp(h, self.w_gate_up, self.alpha, self.limit), self.w_down)
         if norm is None and residual is None:
             return self.ops.linear(self.ops.linear_swiglu(h, self.w_gate_up), self.w_down)
         act = self.ops.linear_swiglu(h, self.w_gate_up, norm=norm)

@@ -51,6 +51,9 @@ class EmulatedOps:
         u = gu[:, inter:].float().clamp(min=-limit, max=limit)
         return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
 
+    def linear_gated_clamp(self, h, w_gate_up, alpha, limit):
+        return self.gated_clamp(self.linear(h, w_gate_up), alpha, limit)
+
     def tanh(self, x):
         return torch.tanh(x.float()).to(x.dtype)
 

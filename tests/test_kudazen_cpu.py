@@ -115,3 +115,20 @@ def test_greedy_generation_through_the_entry_point(folders):
     engine = Engine.from_session(session(folders["C"]), use_graphs=False)
     assert engine.generate_all(prompts, 12) == want
     assert engine.session.cache.slots.n_held == 0
+
+
+def test_random_weights_from_the_command_line(tmp_path):
+    from starter_b200.cli import main
+    (tmp_path / "config.json").write_text(json.dumps(cases.CASES["C"]))
+    assert main(["random-weights", "--config", str(tmp_path / "config.json"), "--seed", "3", "--out", str(tmp_path / "model")]) == 0
+    sess = session(tmp_path / "model")
+    assert sess.model.spec.vocab_size == 97 and len(sess.model.blocks) == 3
+    seqs = random_tokens(97, (12,), seed=8)
+    assert_close(run_whole(sess, seqs), cases.plain_logits(tmp_path / "model", seqs, "float32"), "float32", "folder from the command line")
+
+
+def test_replay_sizes_its_cache_for_whole_pages():
+    from starter_b200.engine.replay import cache_room
+    tokens, slots = cache_room(1728, 128)
+    assert slots == 128 and tokens >= 1728 + 128 * 63        # every live request may leave a page all but empty
+    assert cache_room(5, 128) == (5 + 5 * 63, 5)              # never more requests than tokens

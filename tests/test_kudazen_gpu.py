@@ -72,7 +72,8 @@ def run_mixer(rt, part, h, cuts, max_step_tokens=1024):
 
 
 def cuttings(n):
-    return [[n], [n - 9] + [1] * 9, [2] * (n // 2) + [1] * (n % 2), [n // 3, n - n // 3]]
+    """Whole; a tail token by token; portions of two; two unequal portions; every token alone."""
+    return [[n], [n - 9] + [1] * 9, [2] * (n // 2) + [1] * (n % 2), [n // 3, n - n // 3], [1] * n]
 
 
 # ---- row-wise kernels --------------------------------------------------------------------------------------
@@ -101,7 +102,7 @@ def test_feed_forward_with_clamps(mode):
     spec = GatedMLPSpec(hidden_size=72, intermediate_size=200, activation="clamped_swish", limit=0.75, alpha=1.702)
     w = {"gate": rand((200, 72), 4, 0.2), "up": rand((200, 72), 5, 0.2), "down": rand((72, 200), 6, 0.1)}
     part = build_part("ff", spec, {k: v.to(rt.dtype).cuda() for k, v in w.items()}, rt)
-    for rows in (3, 40):
+    for rows in (3, 16, 40):      # few rows: the activation sits in the decode product's epilogue (bfloat16)
         h = rand((rows, 72), 7)
         gate = h @ w["gate"].T
         assert float(gate.max()) > 0.75 and float((h @ w["up"].T).min()) < -0.75       # the clamps bite
@@ -341,3 +342,47 @@ def test_greedy_generation_through_the_entry_point(folders, dtype, graphs):
                 break
             seq.append(tok)
     assert engine.session.cache.slots.n_held == 0
+
+
+def test_replay_of_a_trace_through_the_command(folders, tmp_path):
+    """bin/trace_run on a Kudazen folder: requests alone and whole, a batch of unequal requests that is then decoded
+    together (the shorter ones end earlier), logits only where they are wanted."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    folder, vocab = folders["A", "bfloat16"], 211
+    seqs = random_tokens(vocab, (70, 9, 131), seed=14)
+    ref = cases.plain_logits(folder, seqs, "bfloat16")
+    steps = [{"step": i, "entries": [{"id": f"w{i}", "tokens": s, "want": [0, len(s) - 1]}], "end": [f"w{i}"]} for i, s in enumerate(seqs)]
+    cut = [len(s) - 6 for s in seqs]
+    cut[1] = 1
+    steps.append({"step": 3, "entries": [{"id": f"b{i}", "tokens": s[:cut[i]], "want": [cut[i] - 1]} for i, s in enumerate(seqs)], "end": []})
+    expect = {3: [(i, cut[i] - 1) for i in range(3)]}
+    for t in range(8):
+        live = [i for i in range(3) if cut[i] + t < len(seqs[i])]
+        steps.append({"step": 4 + t, "entries": [{"id": f"b{i}", "tokens": [seqs[i][cut[i] + t]], "want": [0] if t % 2 == 0 else []} for i in live],
+                      "end": [f"b{i}" for i in live if cut[i] + t + 1 == len(seqs[i])]})
+        if t % 2 == 0:
+            expect[4 + t] = [(i, cut[i] + t) for i in live]
+    text = "".join(json.dumps(st) + "\n" for st in steps)
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "bfloat16", "--out",
+                           str(tmp_path), "--max-tokens", str(sum(len(s) for s in seqs))], input=text, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for st in steps for w in ("done", str(st["step"]))]
+    scale = max(float(r.abs().max()) for r in ref)
+
+    def read(step):
+        return torch.from_numpy(np.fromfile(tmp_path / f"{step}.f32", dtype="<f4").reshape(-1, vocab).copy())
+    for i, r in enumerate(ref):
+        got = read(i)
+        assert got.shape[0] == 2 and float((got - r[[0, len(r) - 1]]).abs().max()) <= 2e-2 * scale
+    for step, rows in expect.items():
+        got = read(step)
+        assert got.shape[0] == len(rows)
+        for j, (i, pos) in enumerate(rows):
+            assert float((got[j] - ref[i][pos]).abs().max()) <= 2e-2 * scale, f"step {step}, request {i}, position {pos}"
+    assert not (tmp_path / "5.f32").exists()
