@@ -110,10 +110,11 @@ def test_feed_forward_with_clamps(mode):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_product_per_head_on_views(mode):
+@pytest.mark.parametrize("rows", [5, 16, 37, 200])      # a warp per column; tiles of 64 rows; the library's batched product (bfloat16)
+def test_product_per_head_on_views(mode, rows):
     rt = runtime(mode)
-    a, w = rand((37, 3, 24 + 8), 1), rand((3, 56, 24), 2, 0.2)
-    out = torch.full((37, 3, 56 + 8), 7.0, dtype=rt.dtype, device="cuda")
+    a, w = rand((rows, 3, 24 + 8), 1), rand((3, 56, 24), 2, 0.2)
+    out = torch.full((rows, 3, 56 + 8), 7.0, dtype=rt.dtype, device="cuda")
     rt.ops.linear_heads(a.to(rt.dtype).cuda()[:, :, :24], w.to(rt.dtype).cuda(), out[:, :, :56])
     close(out[:, :, :56], torch.einsum("rhk,hnk->rhn", a[:, :, :24], w), mode, "per-head product")
     assert bool((out[:, :, 56:] == 7.0).all())
