@@ -20,9 +20,27 @@ __global__ void embed_wide_kernel(const int* __restrict__ tokens, const __nv_bfl
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = __bfloat162float(src[c]);
 }
 
+// Four consecutive values of a row as floats, whatever the type they are stored in.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned int*>(&a);
+    raw.y = *reinterpret_cast<const unsigned int*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // One block per row.  x <- x + (d1 + d2) first when deltas are given (either may be null); then every group of
 // width / groups consecutive columns is divided by its own root mean square and multiplied by the weight.
-template <class TX, class T, class W>
+// VEC: the group's width is a multiple of 4, so a thread takes four columns at a time (16-byte reads of a 32-bit row).
+template <class TX, class T, class W, bool VEC>
 __global__ void grouped_rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ d1, const T* __restrict__ d2,
                                        const W* __restrict__ weight, T* __restrict__ out, int width, int groups, float eps) {
     __shared__ float red[33];
@@ -34,20 +52,45 @@ __global__ void grouped_rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__
     for (int g = 0; g < groups; ++g) {
         const int c0 = g * gw, c1 = c0 + gw;
         float ss = 0.f;
-        for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
-            float v = to_f<TX>(xr[c]);
-            if (d1 != nullptr) {
-                float d = to_f<T>(d1[base + c]);
-                if (d2 != nullptr) d = __fadd_rn(d, to_f<T>(d2[base + c]));
-                v = rnd<TX>(__fadd_rn(v, d));
-                xr[c] = from_f<TX>(v);
+        if (VEC) {
+            for (int c = c0 + 4 * threadIdx.x; c < c1; c += 4 * blockDim.x) {
+                float4 v = load4(xr + c);
+                if (d1 != nullptr) {
+                    float4 d = load4(d1 + base + c);
+                    if (d2 != nullptr) {
+                        const float4 e = load4(d2 + base + c);
+                        d = make_float4(__fadd_rn(d.x, e.x), __fadd_rn(d.y, e.y), __fadd_rn(d.z, e.z), __fadd_rn(d.w, e.w));
+                    }
+                    v = make_float4(rnd<TX>(__fadd_rn(v.x, d.x)), rnd<TX>(__fadd_rn(v.y, d.y)), rnd<TX>(__fadd_rn(v.z, d.z)),
+                                    rnd<TX>(__fadd_rn(v.w, d.w)));
+                    store4(xr + c, v);
+                }
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
             }
-            ss = fmaf(v, v, ss);
+        } else {
+            for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
+                float v = to_f<TX>(xr[c]);
+                if (d1 != nullptr) {
+                    float d = to_f<T>(d1[base + c]);
+                    if (d2 != nullptr) d = __fadd_rn(d, to_f<T>(d2[base + c]));
+                    v = rnd<TX>(__fadd_rn(v, d));
+                    xr[c] = from_f<TX>(v);
+                }
+                ss = fmaf(v, v, ss);
+            }
         }
         ss = block_sum(ss, red);
         const float rstd = 1.0f / sqrtf(ss / (float)gw + eps);
-        for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x)
-            out[base + c] = from_f<T>(__fmul_rn(__fmul_rn(to_f<TX>(xr[c]), rstd), to_f<W>(weight[c])));
+        if (VEC) {
+            for (int c = c0 + 4 * threadIdx.x; c < c1; c += 4 * blockDim.x) {   // the thread's own four values again: still in L1
+                const float4 v = load4(xr + c), w4 = load4(weight + c);
+                store4(out + base + c, make_float4(__fmul_rn(__fmul_rn(v.x, rstd), w4.x), __fmul_rn(__fmul_rn(v.y, rstd), w4.y),
+                                                   __fmul_rn(__fmul_rn(v.z, rstd), w4.z), __fmul_rn(__fmul_rn(v.w, rstd), w4.w)));
+            }
+        } else {
+            for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x)
+                out[base + c] = from_f<T>(__fmul_rn(__fmul_rn(to_f<TX>(xr[c]), rstd), to_f<W>(weight[c])));
+        }
     }
 }
 
@@ -110,11 +153,20 @@ int sb_grouped_rmsnorm(int x_dtype, int dtype, int w_dtype, void* x, const void*
                        int rows, int width, int groups, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (groups < 1 || width % groups) return (int)cudaErrorInvalidValue;
-    const int threads = width / groups >= 1024 ? 256 : 128;
+    const int gw = width / groups;
+    const bool vec = gw % 4 == 0;
+    int threads = vec ? (gw / 4 + 31) / 32 * 32 : (gw >= 1024 ? 256 : 128);
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
     typedef __nv_bfloat16 bf;
-#define SB_GN(TX, T, W)                                                                                                 \
-    sb_launch(grouped_rmsnorm_kernel<TX, T, W>, rows, threads, 0, stream, (TX*)x, (const T*)d1, (const T*)d2, (const W*)weight, \
-              (T*)out, width, groups, eps)
+#define SB_GN(TX, T, W)                                                                                                        \
+    do {                                                                                                                       \
+        if (vec)                                                                                                               \
+            sb_launch(grouped_rmsnorm_kernel<TX, T, W, true>, rows, threads, 0, stream, (TX*)x, (const T*)d1, (const T*)d2,    \
+                      (const W*)weight, (T*)out, width, groups, eps);                                                          \
+        else                                                                                                                   \
+            sb_launch(grouped_rmsnorm_kernel<TX, T, W, false>, rows, threads, 0, stream, (TX*)x, (const T*)d1, (const T*)d2,   \
+                      (const W*)weight, (T*)out, width, groups, eps);                                                          \
+    } while (0)
     if (x_dtype == SB_F32 && dtype == SB_F32 && w_dtype == SB_F32) SB_GN(float, float, float);
     else if (x_dtype == SB_F32 && dtype == SB_BF16 && w_dtype == SB_BF16) SB_GN(float, bf, bf);
     else if (x_dtype == SB_F32 && dtype == SB_BF16 && w_dtype == SB_F32) SB_GN(float, bf, float);
