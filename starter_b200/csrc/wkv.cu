@@ -32,6 +32,55 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
     }
 }
 
+// bfloat16 rows and blend vectors whose width is a multiple of 8: eight columns per thread, 16-byte accesses.
+__global__ void token_shift_vec_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ state, long long state_stride,
+                                       int prev_offset, const __nv_bfloat16* __restrict__ mu, int n_mix, SbBatch batch, int width,
+                                       __nv_bfloat16* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const int s = batch.row_seq[row];
+    const bool first = row == batch.cu_q[s];
+    const float* rec = state + (long long)batch.seq_slot[s] * state_stride + prev_offset;
+    const __nv_bfloat16* cur = h + (long long)row * width;
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        float x[8], d[8];
+        const uint4 raw = *reinterpret_cast<const uint4*>(cur + c);
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(xh[e]);
+            x[2 * e] = f.x;
+            x[2 * e + 1] = f.y;
+        }
+        if (first) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d[e] = rec[c + e] - x[e];
+        } else {
+            const uint4 praw = *reinterpret_cast<const uint4*>(cur + c - width);
+            const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&praw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(ph[e]);
+                d[2 * e] = f.x - x[2 * e];
+                d[2 * e + 1] = f.y - x[2 * e + 1];
+            }
+        }
+        for (int m = 0; m < n_mix; ++m) {
+            const uint4 mraw = *reinterpret_cast<const uint4*>(mu + (long long)m * width + c);
+            const __nv_bfloat162* mh = reinterpret_cast<const __nv_bfloat162*>(&mraw);
+            uint4 res;
+            __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(mh[e]);
+                rh[e] = __floats2bfloat162_rn(fmaf(d[2 * e], f.x, x[2 * e]), fmaf(d[2 * e + 1], f.y, x[2 * e + 1]));
+            }
+            *reinterpret_cast<uint4*>(out + ((long long)m * batch.n_rows + row) * width + c) = res;
+        }
+    }
+}
+
 #define WKV_TB 32   // tokens whose r, k, v and decay are staged in shared memory at a time
 #define WKV_IG 8    // threads that share a group of value channels: each holds D / 8 key channels of those columns of the state
 #define WKV_CJ 1    // value channels (columns of the state) per thread
@@ -183,6 +232,11 @@ int sb_token_shift(int dtype, int w_dtype, const void* h, const float* state, lo
     if (batch.n_rows <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     typedef __nv_bfloat16 bf;
+    if (dtype == SB_BF16 && w_dtype == SB_BF16 && width % 8 == 0) {
+        sb_launch(token_shift_vec_kernel, batch.n_rows, threads, 0, stream, (const bf*)h, state, state_stride, prev_offset,
+                  (const bf*)mu, n_mix, batch, width, (bf*)out);
+        SB_LAUNCH_CHECK();
+    }
 #define SB_TS(T, W)                                                                                                        \
     sb_launch(token_shift_kernel<T, W>, batch.n_rows, threads, 0, stream, (const T*)h, state, state_stride, prev_offset, (const W*)mu, \
               n_mix, batch, width, (T*)out)
