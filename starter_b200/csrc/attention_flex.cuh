@@ -2,7 +2,7 @@
 #pragma once
 #include "common.cuh"
 
-#define FLEX_MAX_V 512   // widest value row of the general kernel
+#define FLEX_MAX_V 1024   // widest value row of the general kernel
 
 // q is a view [rows, heads, k_dim] with a row stride and a head stride (elements).  Keys: pages
 // [page][kv_head][SB_PAGE][k_dim].  Values: pages [page][kv_head][SB_PAGE][v_row] of which the first v_dim columns

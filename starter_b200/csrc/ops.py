@@ -776,8 +776,8 @@ class Ops:
             raise KernelError(f"{H} query heads cannot share {layer_cache.group.request.num_kv_heads} key/value heads evenly")
         p = self._flex(layer_cache, q, H, scale, v_dim, values_in_keys, sink, head_scale, slopes, chunk, window)
         out = torch.empty((rows, H * v_dim), dtype=q.dtype, device=q.device)
-        if v_dim > 512:
-            raise KernelError(f"attention takes values of up to 512 columns, not {v_dim}")
+        if v_dim > 1024:
+            raise KernelError(f"attention takes values of up to 1024 columns, not {v_dim}")
         if self._flex_takes_rows64(ctx, q, p, values_in_keys):
             self._check(self.lib.sb_flex_attention_rows64(p, self._batch(ctx), _ptr(out), ctx.max_q_len, int(values_in_keys),
                                                           self._stream()), "flex_attention_rows64")
@@ -902,8 +902,8 @@ class Ops:
         """The recurrence over every sequence's rows, from and back into ``state``; returns the heads' outputs after the
         unit norm, the scale and the gate [rows, heads * dim].  Also leaves each sequence's last row of h in its record."""
         inner = heads * dim
-        if dim > 128:
-            raise KernelError(f"the recurrence takes heads of up to 128 channels, not {dim}")
+        if dim > 4096:
+            raise KernelError(f"the recurrence takes heads of up to 4096 channels, not {dim}")
         for t in (r, k, v, g):
             if tuple(t.shape) != (h.shape[0], inner) or not t.is_contiguous() or t.dtype != h.dtype:
                 raise KernelError("wkv_scan: r, k, v, g are contiguous [rows, heads * dim] in the run's dtype")

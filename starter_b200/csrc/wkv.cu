@@ -225,6 +225,61 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
     }
 }
 
+// Heads of more than 128 channels: the state stays in global memory (it is the sequence's record anyway), thread j owns
+// value channel j and walks the key channels of its column token by token.  Slow and plain; the sizes models have go
+// through the kernel above.
+template <class T>
+__global__ void wkv_scan_wide_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
+                                     const float* __restrict__ decay_pre, const float* __restrict__ w0, const float* __restrict__ u,
+                                     const float* __restrict__ norm_w, float eps, const T* __restrict__ h, int width,
+                                     float* __restrict__ state, long long state_stride, int prev_offset, SbBatch batch, int H, int D,
+                                     T* __restrict__ y) {
+    extern __shared__ float sm[];
+    float* rs = sm;          // the token's r, k and decay, [D] each
+    float* ks = rs + D;
+    float* ws = ks + D;
+    float* os = ws + D;      // the token's raw outputs
+    __shared__ float red[33];
+    pdl_wait();
+    const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int slot = batch.seq_slot[s], row0 = batch.cu_q[s], row1 = batch.cu_q[s + 1];
+    const int HD = H * D;
+    float* Sg = state + (long long)slot * state_stride + (long long)head * D * D;
+    for (int t = row0; t < row1; ++t) {
+        const long long at = (long long)t * HD + head * D;
+        __syncthreads();
+        for (int i = tid; i < D; i += blockDim.x) {
+            rs[i] = to_f<T>(r[at + i]);
+            ks[i] = to_f<T>(k[at + i]);
+            ws[i] = expf(-expf(decay_pre[at + i] + w0[head * D + i]));
+        }
+        __syncthreads();
+        float ss = 0.f;
+        for (int j = tid; j < D; j += blockDim.x) {   // the same thread owns column j at every token: nobody else touches it
+            const float vj = to_f<T>(v[at + j]);
+            float o = 0.f;
+            for (int i = 0; i < D; ++i) {
+                const float old = Sg[(long long)i * D + j], kv = ks[i] * vj;
+                o = fmaf(rs[i], fmaf(u[head * D + i], kv, old), o);
+                Sg[(long long)i * D + j] = fmaf(ws[i], old, kv);
+            }
+            os[j] = o;
+            ss = fmaf(o, o, ss);
+        }
+        ss = block_sum(ss, red);
+        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int j = tid; j < D; j += blockDim.x) {
+            const float gv = to_f<T>(g[at + j]);
+            y[at + j] = from_f<T>(os[j] * rstd * norm_w[head * D + j] * (gv / (1.0f + expf(-gv))));
+        }
+    }
+    if (head == 0 && row1 > row0) {
+        float* rec = state + (long long)slot * state_stride + prev_offset;
+        const T* last = h + (long long)(row1 - 1) * width;
+        for (int c = tid; c < width; c += blockDim.x) rec[c] = to_f<T>(last[c]);
+    }
+}
+
 extern "C" {
 
 int sb_token_shift(int dtype, int w_dtype, const void* h, const float* state, long long state_stride, int prev_offset, const void* mu,
@@ -252,7 +307,20 @@ int sb_wkv_scan(int dtype, const void* r, const void* k, const void* v, const vo
                 const float* u, const float* norm_w, float eps, const void* h, int width, float* state, long long state_stride,
                 int prev_offset, SbBatch batch, int H, int D, void* y, cudaStream_t stream) {
     if (batch.n_seqs <= 0 || batch.n_rows <= 0) return 0;
-    if (D < 1 || D > 128 || H > 65535) return (int)cudaErrorInvalidValue;
+    if (D < 1 || D > 4096 || H > 65535) return (int)cudaErrorInvalidValue;
+    if (D > 128) {
+        dim3 wide(batch.n_seqs, H);
+        const int wt = D < 1024 ? (D + 31) / 32 * 32 : 1024;
+        if (dtype == SB_F32)
+            sb_launch(wkv_scan_wide_kernel<float>, wide, wt, (size_t)4 * D * sizeof(float), stream, (const float*)r, (const float*)k,
+                      (const float*)v, (const float*)g, decay_pre, w0, u, norm_w, eps, (const float*)h, width, state, state_stride,
+                      prev_offset, batch, H, D, (float*)y);
+        else
+            sb_launch(wkv_scan_wide_kernel<__nv_bfloat16>, wide, wt, (size_t)4 * D * sizeof(float), stream, (const __nv_bfloat16*)r,
+                      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)g, decay_pre, w0, u, norm_w, eps,
+                      (const __nv_bfloat16*)h, width, state, state_stride, prev_offset, batch, H, D, (__nv_bfloat16*)y);
+        SB_LAUNCH_CHECK();
+    }
     dim3 grid(batch.n_seqs, H);
     const size_t smem = (size_t)(6 * WKV_TB + 2) * D * sizeof(float);
     const int threads = ((D + WKV_CJ - 1) / WKV_CJ * WKV_IG + 31) / 32 * 32;

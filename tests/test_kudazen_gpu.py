@@ -152,7 +152,7 @@ def test_latent_attention_alone(mode, sizes):
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("H, D, rank", [(2, 24, 8), (4, 32, 16), (1, 40, 5), (2, 64, 32), (1, 128, 16)])
+@pytest.mark.parametrize("H, D, rank", [(2, 24, 8), (4, 32, 16), (1, 40, 5), (2, 64, 32), (1, 128, 16), (1, 160, 8)])
 def test_wkv_alone(mode, H, D, rank):
     rt, rnd = runtime(mode), plain.rounder(mode)
     width, inner = 72, H * D
