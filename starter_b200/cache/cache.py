@@ -15,7 +15,8 @@ with one batch row per sequence and a device ``pos[batch]``
 * one extra **null slot** with one null page takes the writes of padding rows.
 
 Page layout of a key/value group: ``[layer_in_group, page, kv_head, PAGE, head_dim]`` (values: ``v_dim`` columns,
-the same as ``head_dim`` unless the mixer asks otherwise; none at all for ``v_dim`` 0).
+the same as ``head_dim`` unless the mixer asks otherwise; none at all for ``v_dim`` 0; ``v_heads`` heads when
+several key heads read the same values).
 Position p of a sequence lives in logical page ``p // PAGE`` at offset
 ``p % PAGE``; logical page j is physical page ``table[slot, j]`` for a full
 group and ``table[slot, j % ring_pages]`` for a window group.
@@ -38,12 +39,15 @@ PAGE = 64
 class KVRequest:
     """A mixer's need for keys and values: every key (window None) or the last ``window``.  ``v_dim``: columns of a
     value when they differ from the key's ``head_dim``; 0 keeps no values at all (a mixer that reads its values out
-    of the cached key rows)."""
+    of the cached key rows).  ``v_heads``: value heads when they are fewer than key heads (it divides
+    ``num_kv_heads``; key head c reads value head c // (num_kv_heads / v_heads): a mixer with several score maps
+    over the same values)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None
+    v_heads: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -81,8 +85,11 @@ class KVGroup:
         self.null_page = pool_pages
         shape = (len(self.layers), pool_pages + 1, request.num_kv_heads, PAGE, request.head_dim)
         self.v_dim = request.head_dim if request.v_dim is None else int(request.v_dim)
+        self.v_heads = request.num_kv_heads if request.v_heads is None else int(request.v_heads)
+        if self.v_heads < 1 or request.num_kv_heads % self.v_heads:
+            raise CacheError(f"{request.num_kv_heads} key heads cannot share {self.v_heads} value heads evenly")
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape[:-1] + (self.v_dim,), dtype=dtype, device=device) if self.v_dim else None
+        self.v = torch.zeros(shape[:2] + (self.v_heads, PAGE, self.v_dim), dtype=dtype, device=device) if self.v_dim else None
         self.pages = IndexAllocator(pool_pages, "cache page")
         self.table_host = torch.full((n_slots + 1, self.table_width), -1, dtype=torch.int32)
         self.table_host[n_slots, :] = self.null_page

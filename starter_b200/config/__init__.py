@@ -2,10 +2,12 @@
 
 from .registry import (ConfigError, ModelConfig, TensorNames, architecture_names, config_from_dict, load_config,
                        register_architecture, save_config)
-from .specs import (AttentionSpec, BiasedAttentionSpec, BlockSpec, GatedMLPSpec, GroupedNormSpec, LatentAttentionSpec,
-                    ModelSpec, NormSpec, PairRopeSpec, ParallelBlockSpec, RopeSpec, WKVSpec)
+from .specs import (AttentionSpec, BiasedAttentionSpec, BlockSpec, DiffAttentionSpec, GatedMLPSpec, GLASpec, GroupedNormSpec,
+                    LatentAttentionSpec, ModelSpec, MoESpec, NormSpec, PairRopeSpec, ParallelBlockSpec, RopeSpec,
+                    ScaledHalfRopeSpec, StreamBlockSpec, StreamNormSpec, WKVSpec)
 
 __all__ = ["ConfigError", "ModelConfig", "TensorNames", "architecture_names", "config_from_dict", "load_config",
            "register_architecture", "save_config", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
            "NormSpec", "RopeSpec", "BiasedAttentionSpec", "GroupedNormSpec", "LatentAttentionSpec", "PairRopeSpec",
-           "ParallelBlockSpec", "WKVSpec"]
+           "ParallelBlockSpec", "WKVSpec", "DiffAttentionSpec", "GLASpec", "MoESpec", "ScaledHalfRopeSpec", "StreamBlockSpec",
+           "StreamNormSpec"]

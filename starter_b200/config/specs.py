@@ -54,6 +54,23 @@ class PairRopeSpec:
 
 
 @dataclass(frozen=True)
+class ScaledHalfRopeSpec:
+    """Rotary position encoding over the first ``rotary_dim`` columns of a head, column i paired with column
+    i + rotary_dim/2, with 32-bit angles taken in the kernels (no table) and, when ``factor`` is given, frequencies
+    stretched by wavelength: with d(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta), pairs below d(fast) keep
+    f_i = theta**(-2i / rotary_dim), pairs above d(slow) turn ``factor`` times slower, a linear ramp in between, and
+    cosines and sines grow by 0.1 ln(factor) + 1."""
+
+    theta: float
+    rotary_dim: int
+    factor: Optional[float] = None
+    original: Optional[float] = None
+    fast: Optional[float] = None
+    slow: Optional[float] = None
+    kind: str = "rope_half_scaled"
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Causal grouped-query attention over a key/value cache.
 
@@ -98,6 +115,44 @@ class BiasedAttentionSpec:
     chunk: Optional[int] = None
     window: Optional[int] = None
     kind: str = "biased_attention"
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Causal grouped-query attention with two score maps per head over the same values (kind "diff_attention"):
+    queries and keys hold [map 1 | map 2] of ``head_dim`` columns each, every map is a softmax attention of its own, and
+    a head's output is (a1 - lambda a2) divided by its root mean square over ``v_dim`` (eps ``norm_eps``) times
+    (1 - ``diff``), with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` from four learned vectors.  ``window``:
+    only the last ``window`` keys are visible (None: all); ``position``: a position part applied to every map."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_dim: int
+    scale: float
+    diff: float
+    norm_eps: float
+    window: Optional[int] = None
+    position: Optional[Any] = None
+    kind: str = "diff_attention"
+
+
+@dataclass(frozen=True)
+class GLASpec:
+    """Gated linear attention (kind "gla"): per head a [head_dim, v_dim] state S <- diag(a_t) S + k_t v_t^T read as
+    o_t = S^T q_t, with a decay per key channel a = sigmoid(W2 (W1 h) + b)**(1 / tau) through two small matrices of
+    inner size ``decay_rank``; the head's output is RMS-normed over ``v_dim`` with a weight shared by the heads and
+    gated by silu(W_g h)."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_dim: int
+    tau: float
+    decay_rank: int
+    norm_eps: float
+    kind: str = "gla"
 
 
 @dataclass(frozen=True)
@@ -155,6 +210,50 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class MoESpec:
+    """Mixture of experts (kind "moe"): a 32-bit router over ``n_experts`` gated feed-forwards (``expert``: the
+    GatedMLPSpec every one of them has) and ``n_identity`` further outputs that stand for experts which hand their
+    input back.  s = softmax(router logits) over all of them; the ``top`` largest of s + correction are chosen; their
+    weights are their s divided by the chosen ones' sum (+ 1e-20), times ``route_scale``.  ``shared``: a feed-forward
+    that every token runs and that is added."""
+
+    hidden_size: int
+    n_experts: int
+    n_identity: int
+    top: int
+    route_scale: float
+    expert: Any
+    shared: Optional[Any] = None
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
+class StreamNormSpec:
+    """The way a branch meets a residual kept in ``streams`` copies X_1 .. X_S (kind "stream_rmsnorm"): it reads
+    RMSNorm(sum_s in[s] X_s) * weight, and its output y returns as X'_t = sum_s mix[s, t] X_s + mult out[t] y, all
+    streams at once from the old ones, in 32-bit.  ``streams`` 0: one plain residual, x += mult y, no learned
+    in / out / mix."""
+
+    size: int
+    eps: float
+    streams: int = 0
+    mult: float = 1.0
+    kind: str = "stream_rmsnorm"
+
+
+@dataclass(frozen=True)
+class StreamBlockSpec:
+    """One layer over a residual in streams: the mixer, then the feed-forward (which may be absent), each read and
+    written through its own StreamNormSpec."""
+
+    mixer_norm: Any
+    mixer: Any
+    ff_norm: Any = None
+    ff: Any = None
+    kind: str = "streams"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: x += mixer(norm(x)); x += ff(norm(x)) for kind "prenorm"."""
 
@@ -189,6 +288,9 @@ class ModelSpec:
 
     ``residual_float32``: the residual stream is kept and summed in 32-bit also in a bfloat16 run (the norms then
     read 32-bit rows and hand the run's dtype to the branches).
+
+    ``streams``: the residual is kept in this many 32-bit copies side by side ([rows, streams * hidden], all equal to
+    the embedding output at the start, summed before the final norm); the layers are then of kind "streams".
     """
 
     hidden_size: int
@@ -201,6 +303,7 @@ class ModelSpec:
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
     residual_float32: bool = False
+    streams: Optional[int] = None
 
     def execution_order(self) -> Tuple[int, ...]:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

@@ -97,3 +97,43 @@ class ResidualStream:
         if self.pending is not None:
             raise RuntimeError("a branch output is already waiting to be added to the residual")
         self.pending = (branch_output, *more) if more else branch_output
+
+    def at_rows(self, ops, rows: torch.Tensor) -> "ResidualStream":
+        """The stream of the given rows only (what the output head needs): x and whatever waits, gathered."""
+        out = ResidualStream(ops.gather_rows(self.x, rows))
+        if self.pending is not None:
+            deltas = self.pending if isinstance(self.pending, tuple) else (self.pending,)
+            out.push(*(ops.gather_rows(d, rows) for d in deltas))
+        return out
+
+
+class StreamResidual:
+    """A residual kept in ``streams`` 32-bit copies side by side, x [rows, streams * hidden].  A branch's output y
+    returns as X'_t = sum_s mix[s, t] X_s + out[t] * y; the return waits here (``pending`` = (y, mix, out)) and is
+    taken by the kernel of the next read, which blends the streams with the reader's weights and norms the blend."""
+
+    def __init__(self, x: torch.Tensor, streams: int):
+        self.x = x
+        self.streams = int(streams)
+        self.pending = None
+
+    def read(self, ops, read_w, weight, eps, dtype) -> torch.Tensor:
+        pending, self.pending = self.pending, None
+        return ops.stream_norm(self.x, self.streams, pending, read_w, weight, eps, dtype)
+
+    def push_return(self, y, mix, out) -> None:
+        if self.pending is not None:
+            raise RuntimeError("a branch output is already waiting to return to the streams")
+        self.pending = (y, mix, out)
+
+    def normed(self, norm) -> torch.Tensor:
+        """The norm of the sum of the streams (what the output head reads)."""
+        ones = torch.ones(self.streams, dtype=torch.float32, device=self.x.device)
+        return self.read(norm.ops, ones, norm.weight, norm.eps, norm.dtype)
+
+    def at_rows(self, ops, rows: torch.Tensor) -> "StreamResidual":
+        out = StreamResidual(ops.gather_rows(self.x, rows), self.streams)
+        if self.pending is not None:
+            y, mix, o = self.pending
+            out.push_return(ops.gather_rows(y, rows), mix, o)
+        return out

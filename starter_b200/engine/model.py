@@ -14,7 +14,7 @@ import torch
 from ..config.registry import load_config
 from ..parts.registry import build_part, part_class
 from ..weights.loader import Checkpoint, WeightsError
-from .context import ResidualStream, Runtime, StepContext
+from .context import ResidualStream, Runtime, StepContext, StreamResidual
 
 
 class DecoderModel:
@@ -108,8 +108,14 @@ class DecoderModel:
 
     # ---- forward -----------------------------------------------------------------------
 
-    def hidden(self, ctx: StepContext, tokens: torch.Tensor) -> ResidualStream:
+    def hidden(self, ctx: StepContext, tokens: torch.Tensor):
         """Run the step's rows through every layer; returns the residual stream before the final norm."""
+        if self.spec.streams is not None:   # 32-bit copies of the scaled embedding rows, side by side
+            x = ctx.ops.embed_streams(tokens, self.embedding, ctx.status, self.spec.embedding_scale, self.spec.streams)
+            stream = StreamResidual(x, self.spec.streams)
+            for pos, i in enumerate(self.order):
+                self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
+            return stream
         if self.spec.residual_float32 and self.embedding.dtype != torch.float32:
             x = ctx.ops.embed(tokens, self.embedding, ctx.status, out_float32=True)   # the residual stays 32-bit
         else:
@@ -124,12 +130,9 @@ class DecoderModel:
     def logits(self, ctx: StepContext, stream: ResidualStream, rows: Optional[torch.Tensor]) -> torch.Tensor:
         """32-bit logits [len(rows), vocab] at the given rows (all rows when None)."""
         ops = ctx.ops
-        x, delta = stream.x, stream.pending
-        deltas = () if delta is None else (delta if isinstance(delta, tuple) else (delta,))
         if rows is not None:
-            x = ops.gather_rows(x, rows)
-            deltas = tuple(ops.gather_rows(d, rows) for d in deltas)
-        h = self.final_norm.add_forward(x, *deltas) if deltas else self.final_norm.forward(x)
+            stream = stream.at_rows(ops, rows)
+        h = stream.normed(self.final_norm)   # takes what still waits on the stream first
         logits = ops.linear(h, self.lm_head, out_float32=True)
         if self.spec.logit_scale is not None:
             logits = logits * self.spec.logit_scale

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers every architecture it holds."""
 
-from . import kudazen, qwen3  # noqa: F401
+from . import kudazen, nazulorn, qwen3  # noqa: F401

@@ -8,6 +8,8 @@ so the table holds D/2 columns.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .registry import register_part
@@ -65,5 +67,41 @@ class PairRotary:
         pass
 
 
+class ScaledHalfRotary:
+    """Kind "rope_half_scaled": column i of the first ``rotary_dim`` turns with column i + rotary_dim/2; frequencies
+    stretched by wavelength when the spec gives a factor (see ScaledHalfRopeSpec).  No table: ``half_rotary`` hands the
+    kernels 32-bit frequencies, and they take angle = position * frequency, sine and cosine in 32-bit."""
+
+    @staticmethod
+    def weight_shapes(spec):
+        return {}
+
+    def __init__(self, spec, weights, runtime):
+        dims = int(spec.rotary_dim)
+        if dims <= 0 or dims % 2:
+            raise ValueError(f"rotary_dim must be positive and even, got {spec.rotary_dim}")
+        self.rotary_dim = dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = float(spec.theta) ** (-2.0 * i / dims)
+        self.magnitude = 1.0
+        if spec.factor is not None:
+            def pair_at(turns):
+                return dims * math.log(float(spec.original) / (2.0 * math.pi * float(turns))) / (2.0 * math.log(float(spec.theta)))
+            lo = max(math.floor(pair_at(spec.fast)), 0)
+            hi = min(math.ceil(pair_at(spec.slow)), dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / float(spec.factor) * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(float(spec.factor)) + 1.0
+        self.frequencies = f.to(torch.float32).to(runtime.device)
+
+    def prepare(self, n_positions: int) -> None:
+        pass
+
+    def half_rotary(self):
+        """(frequencies [rotary_dim / 2] 32-bit, rotary_dim, what multiplies cosines and sines)."""
+        return self.frequencies, self.rotary_dim, self.magnitude
+
+
 register_part("position", "rope", RotaryEmbedding)
+register_part("position", "rope_half_scaled", ScaledHalfRotary)
 register_part("position", "rope_pairs", PairRotary)

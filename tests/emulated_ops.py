@@ -130,7 +130,7 @@ class EmulatedOps:
             page, off = self._physical(group, slots[r].expand(keys.numel()), keys)
             kk = layer_cache.k[page, :, off].float()                               # [n, G, Kd]
             vv = kk[..., :v_dim] if values_in_keys else layer_cache.v[page, :, off].float()
-            kk, vv = kk.repeat_interleave(H // G, dim=1), vv.repeat_interleave(H // G, dim=1)
+            kk, vv = kk.repeat_interleave(H // G, dim=1), vv.repeat_interleave(H // vv.shape[1], dim=1)
             s = torch.einsum("hd,nhd->hn", qf[r], kk) * scale
             if head_scale is not None:
                 s = s * head_scale.float()[:, None]
@@ -176,6 +176,89 @@ class EmulatedOps:
         o = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)).reshape(-1, H * D)
         gf = g.float()
         return (o * norm.float() * (gf * torch.sigmoid(gf))).to(r.dtype)
+
+    # ---- streams, two-map attention, gated linear attention, experts ----------------------
+
+    def embed_streams(self, tokens, table, status, scale, copies):
+        rows = self.embed(tokens, table, status).float()
+        if scale is not None:
+            rows = rows * scale
+        return rows.repeat(1, copies).contiguous()
+
+    def stream_norm(self, x, streams, pending, read_w, weight, eps, out_dtype):
+        rows = x.shape[0]
+        X = x.view(rows, streams, -1)
+        if pending is not None:
+            y, mix, out = pending
+            new = torch.einsum("st,rsw->rtw", mix.float(), X) + out.float()[None, :, None] * y.float()[:, None, :]
+            X.copy_(new)
+        if read_w is None:
+            return None
+        u = torch.einsum("s,rsw->rw", read_w.float(), X)
+        return (u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * weight.float()).to(out_dtype)
+
+    def rotate_half_store(self, ctx, q, k, v, layer_cache, freqs, rot, magnitude):
+        group = layer_cache.group
+        slots, pos = self._positions(ctx)
+
+        def turn(t):
+            t = t.float()
+            if freqs is None or not rot:
+                return t
+            angle = pos.float()[:, None] * freqs.float()[None, :]
+            c, s = (torch.cos(angle) * magnitude)[:, None, :], (torch.sin(angle) * magnitude)[:, None, :]
+            a, b = t[..., :rot // 2], t[..., rot // 2:rot]
+            return torch.cat([a * c - b * s, b * c + a * s, t[..., rot:]], dim=-1)
+
+        page, off = self._physical(group, slots, pos)
+        if bool((page < 0).any()):
+            ctx.status |= 2
+        ok = page >= 0
+        layer_cache.k[page[ok], :, off[ok]] = turn(k)[ok].to(layer_cache.k.dtype)
+        layer_cache.v[page[ok], :, off[ok]] = v.reshape(v.shape[0], group.v_heads, group.v_dim)[ok].to(layer_cache.v.dtype)
+        return turn(q).to(q.dtype)
+
+    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post):
+        rows, per = a.shape[0], heads // kv_heads
+        maps = a.float().view(rows, kv_heads, 2, per, v_dim)
+        o = maps[:, :, 0] - lam * maps[:, :, 1]
+        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * post
+        return o.reshape(rows, heads * v_dim).to(a.dtype)
+
+    def gla_scan(self, ctx, q, k, v, g, z, bias, norm, eps, tau, q_scale, state, heads, dim, vdim):
+        H, D, V = heads, dim, vdim
+        rows = q.shape[0]
+        out = torch.empty(rows, H, V, dtype=torch.float32, device=q.device)
+        cu = ctx.cu_q.tolist()
+        decay = torch.exp(torch.nn.functional.logsigmoid(z.float() + bias.float()) / tau).reshape(rows, H, D)
+        qq, kk, vv = q.float().reshape(rows, H, D) * q_scale, k.float().reshape(rows, H, D), v.float().reshape(rows, H, V)
+        for b in range(ctx.n_seqs):
+            slot = int(ctx.seq_slot[b])
+            S = state[slot].reshape(H, D, V).clone()
+            for t in range(cu[b], cu[b + 1]):
+                S = decay[t][:, :, None] * S + kk[t][:, :, None] * vv[t][:, None, :]
+                out[t] = torch.einsum("hk,hkv->hv", qq[t], S)
+            state[slot] = S.reshape(-1)
+        o = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps) * norm.float()
+        gf = g.float()
+        return (o.reshape(rows, H * V) * (gf * torch.sigmoid(gf))).to(q.dtype)
+
+    def moe_route(self, h, router, correction, top, scale):
+        s = torch.softmax(h.float() @ router.float().T, dim=-1)
+        chosen = torch.topk(s + correction.float(), top, dim=-1).indices
+        picked = torch.gather(s, 1, chosen)
+        return chosen.to(torch.int32), picked / (picked.sum(-1, keepdim=True) + 1e-20) * scale
+
+    def moe_experts(self, h, chosen, weight, w_gate_up, w_down, n_experts, alpha, limit, base):
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device) if base is None else base.float().clone()
+        for r in range(h.shape[0]):
+            for e, w in zip(chosen[r].tolist(), weight[r]):
+                if e >= n_experts:
+                    out[r] += w * h[r].float()
+                else:
+                    act = self.gated_clamp(self.linear(h[r:r + 1], w_gate_up[e]), alpha, limit)
+                    out[r] += w * self.linear(act, w_down[e])[0].float()
+        return out.to(h.dtype)
 
     def gather_rows(self, x, rows):
         return x[rows.long()].clone()
