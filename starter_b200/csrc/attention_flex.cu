@@ -82,8 +82,9 @@ __global__ void flex_attention_general_kernel(SbFlex p, SbBatch batch, T* __rest
         m = m_new;
 #pragma unroll
         for (int j = 0; j < FLEX_MAX_V / 32; ++j) acc[j] *= alpha;
+        const long long vtok = flex_value_token(p, tok, kvh);
         for (int t = 0; t < 32; ++t) {
-            const long long vt = __shfl_sync(0xffffffffu, tok, t);
+            const long long vt = __shfl_sync(0xffffffffu, vtok, t);
             const float wt = __shfl_sync(0xffffffffu, w, t);
             if (vt < 0) continue;
             const T* vr = vbase + vt * p.v_row;

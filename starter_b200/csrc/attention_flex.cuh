@@ -7,7 +7,8 @@
 // q is a view [rows, heads, k_dim] with a row stride and a head stride (elements).  Keys: pages
 // [page][kv_head][SB_PAGE][k_dim].  Values: pages [page][kv_head][SB_PAGE][v_row] of which the first v_dim columns
 // count; for values kept inside the key rows v points at k and v_row is k_dim.  head_scale, slopes and sink are
-// 32-bit per query head, null when the option is off; window and chunk are 0 when off.
+// 32-bit per query head, null when the option is off; window and chunk are 0 when off.  v_heads: value heads per
+// page when they are fewer than key heads (key head c reads value head c / (n_kv_heads / v_heads)); 0 = as many.
 struct SbFlex {
     const void* q;
     long long q_row;
@@ -28,6 +29,7 @@ struct SbFlex {
     int window;
     int chunk;
     float scale;
+    int v_heads;
 };
 
 // First visible key of a query at position pos.
@@ -46,4 +48,16 @@ __device__ __forceinline__ long long flex_token(const SbFlex& p, int slot, int p
     const int page = p.table[(long long)slot * p.table_width + lp];
     if (page < 0) return -1;
     return ((long long)page * p.n_kv_heads + kv_head) * SB_PAGE + (pos % SB_PAGE);
+}
+
+// The value row that belongs to key row `tok` of key head kv_head (the same row unless value heads are fewer).
+__device__ __forceinline__ long long flex_value_token(const SbFlex& p, long long tok, int kv_head) {
+    if (p.v_heads <= 0 || p.v_heads == p.n_kv_heads || tok < 0) return tok;
+    const long long page = tok / ((long long)p.n_kv_heads * SB_PAGE);
+    return (page * p.v_heads + kv_head / (p.n_kv_heads / p.v_heads)) * SB_PAGE + tok % SB_PAGE;
+}
+// First value row of a page for key head kv_head.
+__device__ __forceinline__ long long flex_value_page(const SbFlex& p, int page, int kv_head) {
+    if (p.v_heads <= 0 || p.v_heads == p.n_kv_heads) return ((long long)page * p.n_kv_heads + kv_head) * SB_PAGE;
+    return ((long long)page * p.v_heads + kv_head / (p.n_kv_heads / p.v_heads)) * SB_PAGE;
 }

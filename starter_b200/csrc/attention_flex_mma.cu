@@ -99,7 +99,7 @@ flex_attention_mma_kernel(SbFlex p, SbBatch batch, __nv_bfloat16* __restrict__ o
                                 page >= 0 && key >= key_lo && key <= key_hi);
         }
         if (!values_in_keys) {
-            const bf* vsrc = (const bf*)p.v + tok0 * p.v_row;
+            const bf* vsrc = (const bf*)p.v + flex_value_page(p, page < 0 ? 0 : page, kvh) * p.v_row;
             constexpr int vcpr = VD / 8;
             for (int c = tid; c < FM_KEYS * vcpr; c += FM_THREADS) {
                 const int r = c / vcpr, cc = c % vcpr, key = page_idx * SB_PAGE + r;
@@ -347,7 +347,7 @@ flex_attention_rows64_kernel(SbFlex p, SbBatch batch, __nv_bfloat16* __restrict_
                                 page >= 0 && key >= key_lo && key <= key_hi);
         }
         if (!values_in_keys) {
-            const bf* vsrc = (const bf*)p.v + tok0 * p.v_row;
+            const bf* vsrc = (const bf*)p.v + flex_value_page(p, page < 0 ? 0 : page, kvh) * p.v_row;
             constexpr int vcpr = VD / 8;
             for (int c = tid; c < FM_KEYS * vcpr; c += FM_THREADS) {
                 const int r = c / vcpr, cc = c % vcpr, key = page_idx * SB_PAGE + r;

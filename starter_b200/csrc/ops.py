@@ -48,7 +48,7 @@ class SbFlex(Structure):
     _fields_ = [("q", c_void_p), ("q_row", c_longlong), ("q_head", c_longlong), ("k", c_void_p), ("v", c_void_p),
                 ("table", c_void_p), ("head_scale", c_void_p), ("slopes", c_void_p), ("sink", c_void_p),
                 ("table_width", c_int), ("ring_pages", c_int), ("n_heads", c_int), ("n_kv_heads", c_int), ("k_dim", c_int),
-                ("v_dim", c_int), ("v_row", c_int), ("window", c_int), ("chunk", c_int), ("scale", c_float)]
+                ("v_dim", c_int), ("v_row", c_int), ("window", c_int), ("chunk", c_int), ("scale", c_float), ("v_heads", c_int)]
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -124,6 +124,21 @@ class Ops:
                                c_void_p],
             "sb_wkv_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                             c_void_p, c_int, c_void_p, c_longlong, c_int, SbBatch, c_int, c_int, c_void_p, c_void_p],
+            "sb_embed_streams": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+            "sb_stream_norm": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                               c_int, c_float, c_void_p],
+            "sb_rotate_half_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, SbBatch,
+                                     SbFlex, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
+            "sb_diff_combine": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+            "sb_gla_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
+                            c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int, c_void_p, c_void_p],
+            "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+            "sb_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+            "sb_moe_gather": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+            "sb_moe_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_float, c_void_p],
+            "sb_moe_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p],
@@ -761,7 +776,8 @@ class Ops:
                 raise KernelError("per-head numbers of the attention are 32-bit, one per query head")
         return SbFlex(_ptr(q), q.stride(0) if q is not None else 0, q.stride(1) if q is not None else 0, _ptr(k), _ptr(v),
                       g.table.data_ptr(), _ptr(head_scale), _ptr(slopes), _ptr(sink), g.table_width, g.ring_pages, n_heads,
-                      g.request.num_kv_heads, g.request.head_dim, v_dim, v_row, int(window or 0), int(chunk or 0), float(scale))
+                      g.request.num_kv_heads, g.request.head_dim, v_dim, v_row, int(window or 0), int(chunk or 0), float(scale),
+                      0 if values_in_keys else g.v_heads)
 
     def flex_attention(self, ctx, q, layer_cache, scale, v_dim, values_in_keys=False, sink=None, head_scale=None, slopes=None,
                        chunk=None, window=None):
@@ -847,7 +863,7 @@ class Ops:
         g = layer_cache.group
         G = g.request.num_kv_heads
         if (k.shape[1] != G * g.request.head_dim or v.shape[1] != G * g.v_dim or k.stride(1) != 1 or v.stride(1) != 1
-                or k.dtype != layer_cache.k.dtype or v.dtype != k.dtype):
+                or k.dtype != layer_cache.k.dtype or v.dtype != k.dtype or g.v_heads != G):
             raise KernelError("kv_store: keys or values do not fit the layer's cache")
         p = self._flex(layer_cache)
         self._check(self.lib.sb_kv_store(_code(k.dtype), _ptr(k), k.stride(0), _ptr(v), v.stride(0), self._batch(ctx), p,
@@ -914,6 +930,152 @@ class Ops:
         self._check(self.lib.sb_wkv_scan(_code(h.dtype), _ptr(r), _ptr(k), _ptr(v), _ptr(g), _ptr(decay_pre), _ptr(w0), _ptr(u),
                                          _ptr(norm), float(eps), _ptr(h), h.shape[1], _ptr(state), state.stride(0),
                                          int(prev_offset), self._batch(ctx), heads, dim, _ptr(y), self._stream()), "wkv_scan")
+        return y
+
+    # ---- a residual in streams, two-map attention, gated linear attention, experts -------
+
+    def embed_streams(self, tokens, table, status, scale, copies):
+        """[rows, copies * width] 32-bit: the table's rows by token id, times ``scale``, ``copies`` times side by side."""
+        out = torch.empty((tokens.shape[0], copies * table.shape[1]), dtype=torch.float32, device=table.device)
+        self._check(self.lib.sb_embed_streams(_code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0],
+                                              table.shape[1], table.shape[0], 1.0 if scale is None else float(scale), int(copies),
+                                              _ptr(status), self._stream()), "embed_streams")
+        return out
+
+    def stream_norm(self, x, streams, pending, read_w, weight, eps, out_dtype):
+        """x [rows, streams * width] 32-bit, in place: with ``pending`` = (y, mix [S, S], out [S]) every stream first becomes
+        X'_t = sum_s mix[s, t] X_s + out[t] y; then, with ``read_w`` [S], RMSNorm(sum_s read_w[s] X'_s) * weight is returned
+        in ``out_dtype`` (None without ``read_w``)."""
+        rows, S = x.shape[0], int(streams)
+        width = x.shape[1] // S
+        if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[1] != S * width or not 1 <= S <= 8:
+            raise KernelError("the streams are 32-bit, contiguous, one to eight copies side by side")
+        y = mix = out_w = None
+        if pending is not None:
+            y, mix, out_w = pending
+            if (y.dtype != out_dtype or tuple(y.shape) != (rows, width) or not y.is_contiguous() or mix.dtype != torch.float32
+                    or out_w.dtype != torch.float32 or mix.numel() != S * S or out_w.numel() != S or not mix.is_contiguous()):
+                raise KernelError("a branch output has the run's dtype and one stream's shape; its return weights are 32-bit")
+        n = None
+        if read_w is not None:
+            if read_w.dtype != torch.float32 or read_w.numel() != S or weight.numel() != width:
+                raise KernelError("a stream read takes one 32-bit weight per stream and a norm weight per column")
+            if out_dtype == torch.float32 and weight.dtype != torch.float32:
+                raise KernelError("a float32 run needs float32 norm weights")
+            n = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+        self._check(self.lib.sb_stream_norm(_code(out_dtype), _code(weight.dtype) if weight is not None else _code(out_dtype), _ptr(x),
+                                            _ptr(y), _ptr(mix), _ptr(out_w), _ptr(read_w), _ptr(weight), _ptr(n), rows, width, S,
+                                            float(eps), self._stream()), "stream_norm")
+        return n
+
+    def rotate_half_store(self, ctx, q, k, v, layer_cache, freqs, rot, magnitude):
+        """q [rows, nq, D], k [rows, key heads, D] (views of wider rows, heads side by side) with the first ``rot`` columns
+        of every head turned (column i with column i + rot / 2) by position * ``freqs`` (32-bit, [rot / 2]), cosines and
+        sines times ``magnitude``; the turned keys and v [rows, value heads * value width] go to the layer's cache, the
+        turned queries are returned [rows, nq, D]."""
+        g = layer_cache.group
+        rows, nq, D = q.shape
+        if (D != g.request.head_dim or tuple(k.shape) != (rows, g.request.num_kv_heads, D) or v.shape[1] != g.v_heads * g.v_dim
+                or q.stride(2) != 1 or k.stride(2) != 1 or v.stride(1) != 1 or q.stride(1) != D or k.stride(1) != D
+                or not (q.dtype == k.dtype == v.dtype == layer_cache.k.dtype)):
+            raise KernelError("rotate_half_store: queries, keys or values do not fit the layer's cache")
+        if freqs is None:
+            rot = 0
+        elif freqs.dtype != torch.float32 or freqs.numel() * 2 != rot or rot > D:
+            raise KernelError("rotate_half_store: one 32-bit frequency per pair of turned columns")
+        p = self._flex(layer_cache)
+        out = torch.empty((rows, nq, D), dtype=q.dtype, device=q.device)
+        self._check(self.lib.sb_rotate_half_store(_code(q.dtype), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0),
+                                                  _ptr(out), self._batch(ctx), p, _ptr(freqs), int(rot), float(magnitude), nq,
+                                                  _ptr(ctx.status), self._stream()), "rotate_half_store")
+        return out
+
+    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post):
+        """a [rows, 2 * heads * v_dim], the two maps of every head in the order (key/value head, map, head of the group) ->
+        [rows, heads * v_dim]: (a1 - lam * a2) / sqrt(mean(.^2) + eps) * post, head by head."""
+        rows = a.shape[0]
+        if a.shape[1] != 2 * heads * v_dim or not a.is_contiguous() or heads % kv_heads:
+            raise KernelError("diff_combine: two maps of v_dim columns per head")
+        out = torch.empty((rows, heads * v_dim), dtype=a.dtype, device=a.device)
+        self._check(self.lib.sb_diff_combine(_code(a.dtype), _ptr(a), _ptr(out), rows, heads, kv_heads, v_dim, float(lam), float(eps),
+                                             float(post), self._stream()), "diff_combine")
+        return out
+
+    def gla_scan(self, ctx, q, k, v, g, z, bias, norm, eps, tau, q_scale, state, heads, dim, vdim):
+        """The gated linear recurrence over every sequence's rows, from and back into ``state`` [slots, heads * dim * vdim];
+        q, k [rows, heads * dim] and v, g [rows, heads * vdim] may be views of the same wider rows; z [rows, heads * dim] is
+        32-bit.  Returns RMSNorm_head(o) * norm * silu(g), [rows, heads * vdim]."""
+        rows = q.shape[0]
+        ld = q.stride(0)
+        for t, w in ((q, heads * dim), (k, heads * dim), (v, heads * vdim), (g, heads * vdim)):
+            if tuple(t.shape) != (rows, w) or t.stride(1) != 1 or t.stride(0) != ld or t.dtype != q.dtype:
+                raise KernelError("gla_scan: q, k, v, g are views of rows with one stride, in the run's dtype")
+        for t in (z, bias, norm, state):
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise KernelError("gla_scan: decay inputs, norm weight and state are 32-bit and contiguous")
+        if tuple(z.shape) != (rows, heads * dim) or state.shape[1] != heads * dim * vdim or norm.numel() != vdim:
+            raise KernelError("gla_scan: sizes do not fit")
+        y = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        self._check(self.lib.sb_gla_scan(_code(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(z), _ptr(bias), _ptr(norm),
+                                         float(eps), float(tau), float(q_scale), _ptr(state), state.stride(0), self._batch(ctx),
+                                         heads, dim, vdim, _ptr(y), self._stream()), "gla_scan")
+        return y
+
+    def moe_route(self, h, router, correction, top, scale):
+        """(chosen int32 [rows, top], weight 32-bit [rows, top]) of softmax(h router^T) (32-bit): the ``top`` largest of
+        score + correction, weighted by their scores over the chosen scores' sum, times ``scale``."""
+        rows, width = h.shape
+        n_out = router.shape[0]
+        if (router.dtype != torch.float32 or correction.dtype != torch.float32 or router.shape[1] != width or not h.is_contiguous()
+                or not router.is_contiguous() or correction.numel() != n_out or n_out > 1024 or top > 32):
+            raise KernelError("moe_route: a 32-bit router of up to 1024 outputs, up to 32 choices")
+        chosen = torch.empty((rows, top), dtype=torch.int32, device=h.device)
+        weight = torch.empty((rows, top), dtype=torch.float32, device=h.device)
+        self._check(self.lib.sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weight), rows,
+                                          width, n_out, int(top), float(scale), self._stream()), "moe_route")
+        return chosen, weight
+
+    MOE_PAIRS_MAX = int(os.environ.get("STARTER_B200_MOE_PAIRS_MAX", 64))   # pairs up to which every pair streams its expert
+
+    def moe_experts(self, h, chosen, weight, w_gate_up, w_down, n_experts, alpha, limit, base):
+        """base + sum_k weight[:, k] * expert_chosen[:, k](h): experts are clamped gated feed-forwards with stacked
+        matrices w_gate_up [experts, 2 ff, width] (gate over up) and w_down [experts, width, ff]; a choice >= n_experts
+        is an identity output and adds weight * h.  A few pairs: each pair streams its expert's matrices (this library's
+        kernels).  Many pairs in bfloat16: the pairs are put in the order of their experts on the device and each matrix
+        takes one grouped product of the vendor's library, as the plain products of a prompt do."""
+        rows, width = h.shape
+        top = chosen.shape[1]
+        pairs = rows * top
+        dt = _code(h.dtype)
+        down = slot_of_pair = None
+        if n_experts > 0:
+            ff = w_down.shape[2]
+            if (tuple(w_gate_up.shape) != (n_experts, 2 * ff, width) or tuple(w_down.shape) != (n_experts, width, ff)
+                    or not w_gate_up.is_contiguous() or not w_down.is_contiguous() or w_gate_up.dtype != h.dtype):
+                raise KernelError("moe_experts: stacked matrices [experts, 2 ff, width] and [experts, width, ff] in the run's dtype")
+            if (h.dtype == torch.bfloat16 and pairs > self.MOE_PAIRS_MAX and width % 8 == 0 and ff % 8 == 0
+                    and hasattr(torch, "_grouped_mm")):
+                ends = torch.empty(n_experts, dtype=torch.int32, device=h.device)
+                slot_of_pair = torch.empty(pairs, dtype=torch.int32, device=h.device)
+                pair_of_slot = torch.empty(pairs, dtype=torch.int32, device=h.device)
+                self._check(self.lib.sb_moe_sort(_ptr(chosen), pairs, n_experts, _ptr(ends), _ptr(slot_of_pair), _ptr(pair_of_slot),
+                                                 self._stream()), "moe_sort")
+                xs = torch.zeros((pairs, width), dtype=h.dtype, device=h.device)
+                self._check(self.lib.sb_moe_gather(dt, _ptr(h), _ptr(pair_of_slot), _ptr(ends), n_experts, pairs, top, width,
+                                                   _ptr(xs), self._stream()), "moe_gather")
+                gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
+                act = self.gated_clamp(gu, alpha, limit)
+                down = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
+            else:
+                act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
+                down = torch.empty((pairs, width), dtype=h.dtype, device=h.device)
+                self._check(self.lib.sb_moe_pairs(dt, _ptr(h), _ptr(chosen), _ptr(w_gate_up), _ptr(w_down), _ptr(act), _ptr(down),
+                                                  pairs, top, n_experts, width, ff, float(alpha), float(limit), self._stream()),
+                            "moe_pairs")
+                self.launches += 1
+        y = torch.empty_like(h)
+        self._check(self.lib.sb_moe_combine(dt, _ptr(h), _ptr(down), _ptr(base), _ptr(chosen), _ptr(weight), _ptr(slot_of_pair),
+                                            _ptr(y), rows, top, n_experts, width, self._stream()), "moe_combine")
         return y
 
     # ---- sampling -----------------------------------------------------------------------

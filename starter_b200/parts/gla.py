@@ -48,9 +48,7 @@ class GatedLinearAttention:
         s, ops, kd, vd = self.spec, self.ops, self.kd, self.vd
         p = ops.linear(h, self.w_in)
         q, k, v, g = p[:, :kd], p[:, kd:2 * kd], p[:, 2 * kd:2 * kd + vd], p[:, 2 * kd + vd:2 * kd + 2 * vd]
-        low = p[:, 2 * kd + 2 * vd:]
-        if low.shape[1] % 8 or (2 * kd + 2 * vd) % 8:
-            low = low.contiguous()     # the products read rows that start on 16 bytes
+        low = p[:, 2 * kd + 2 * vd:].contiguous()     # the products read contiguous rows; this one is decay_rank wide
         z = ops.linear(low, self.w_a2, out_float32=True)
         y = ops.gla_scan(ctx, q, k, v, g, z, self.bias, self.norm, float(s.norm_eps), float(s.tau), float(s.head_dim) ** -0.5,
                          layer_cache.state, s.num_heads, s.head_dim, s.v_dim)
