@@ -419,6 +419,36 @@ FAMILY_SIZES = {
 }
 
 
+def _nazulorn_raw(width, layers, gla, attention, experts, expert_ff, top, identity, shared_ff, vocab=32000, streams=2):
+    """A Nazulorn configuration of ``layers`` layers that cycle through gla, attention, attention."""
+    kinds = [
+        {"type": "gla", "mixer": dict(gla, tau=16.0)},
+        {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5, diff=0.6,
+                                            rot={"base": 1000000.0, "dims": attention["dim"],
+                                                 "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}})},
+    ]
+    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5},
+           "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
+    entries = [dict(kinds[min(i % 3, 1)], mlp=mlp) for i in range(layers)]
+    return {"architecture": "Nazulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.5, "streams": streams, "logit_scale": 1.0, "layers": entries}
+
+
+# Nazulorn beside Kudazen (the closest design the library has: a recurrence with a matrix state, attention with a bounded
+# reach, the clamped activation, a 32-bit residual) at the same width, layers, vocabulary and feed-forward work per token:
+# four chosen experts and the shared expert together are as wide as Kudazen's dense feed-forward; the two maps of a head
+# give the attention kernels Kudazen's number of query and key heads.
+NAZULORN_SIZES = {
+    "1024": (_nazulorn_raw(1024, 6, dict(heads=8, dim=64, vdim=128, decay_rank=64),
+                           dict(heads=8, kv_heads=2, dim=64, vdim=64, mask={"size": 1024}), experts=16, expert_ff=512, top=4,
+                           identity=4, shared_ff=2048), FAMILY_SIZES["1024"][0]),
+    "2048": (_nazulorn_raw(2048, 6, dict(heads=16, dim=64, vdim=128, decay_rank=64),
+                           dict(heads=8, kv_heads=4, dim=128, vdim=128, mask={"size": 2048}), experts=32, expert_ff=1024, top=4,
+                           identity=4, shared_ff=4096), FAMILY_SIZES["2048"][0]),
+}
+FAMILIES = {"kudazen": (FAMILY_SIZES, "qwen3", "Qwen3ForCausalLM"), "nazulorn": (NAZULORN_SIZES, "kudazen", "Kudazen")}
+
+
 class TimedOps:
     """The kernel call table with a pair of CUDA events around every call: per call name, the device time and what
     the call must move or compute at least, from its arguments (the bound is the slower of the two)."""
@@ -457,19 +487,38 @@ class TimedOps:
             for r in (kwargs.get("chunk"), kwargs.get("window"), req.window):
                 if r:
                     reach = min(reach, r)
+            token_bytes = (req.num_kv_heads * req.head_dim + getattr(group, "v_heads", req.num_kv_heads) * (group.v_dim or 0)) * 2
             if ctx.max_q_len == 1:
                 pairs = float(ctx.n_rows) * reach
-                cache_bytes = ctx.n_seqs * reach * req.num_kv_heads * (req.head_dim + (group.v_dim or 0)) * 2
+                cache_bytes = ctx.n_seqs * reach * token_bytes
             else:
                 t = ctx.n_rows / ctx.n_seqs
                 pairs = ctx.n_seqs * (t * (t + 1) / 2.0 if reach >= t else t * reach / 2.0)
-                cache_bytes = ctx.n_rows * req.num_kv_heads * (req.head_dim + (group.v_dim or 0)) * 2
+                cache_bytes = ctx.n_rows * token_bytes
             flops = 2.0 * pairs * heads * (req.head_dim + v_dim)
             nbytes = cache_bytes + 2 * self._nbytes([q]) if name != "qk_attention" else cache_bytes + self._nbytes([q])
         elif name == "wkv_scan":
             r, state, heads, dim = args[1], args[11], args[12], args[13]
             flops = 6.0 * r.shape[0] * heads * dim * dim
             nbytes = 2 * args[0].n_seqs * heads * dim * dim * 4 + 6 * r.numel() * 2
+        elif name == "gla_scan":
+            q, heads, dim, vdim = args[1], args[12], args[13], args[14]
+            flops = 6.0 * q.shape[0] * heads * dim * vdim
+            nbytes = 2 * args[0].n_seqs * heads * dim * vdim * 4 + q.shape[0] * heads * (2 * dim * 2 + 3 * vdim * 2 + dim * 4)
+        elif name == "moe_experts":
+            h, chosen, w_gu, w_down = args[0], args[1], args[3], args[4]
+            pairs = chosen.numel()
+            per_expert = (w_gu[0].numel() + w_down[0].numel()) if w_gu is not None else 0
+            flops = 2.0 * pairs * per_expert      # an upper bound: pairs of identity outputs do no product
+            touched = min(pairs, w_gu.shape[0]) if w_gu is not None else 0
+            nbytes = touched * per_expert * 2 + 3 * h.numel() * 2 + pairs * 8
+        elif name == "moe_route":
+            h, router = args[0], args[1]
+            flops = 0.0    # 32-bit dot products on the CUDA cores: bounded by the rows it reads
+            nbytes = h.numel() * 2 + router.numel() * 4 + h.shape[0] * args[3] * 8
+        elif name == "stream_norm":
+            x, pending = args[0], args[2]
+            nbytes = x.numel() * 4 * (2 if pending is not None else 1) + (x.numel() // args[1]) * 2 * (2 if pending is not None else 1)
         return nbytes, flops
 
     def __getattr__(self, name):
@@ -488,7 +537,8 @@ class TimedOps:
                 label = name
                 if name == "flex_attention":   # the two users of this call apart: values inside the key rows (latent) or pages of their own
                     label += ("[latent]" if kwargs.get("values_in_keys") else
-                              "[latent, narrow form]" if kwargs.get("sink") is not None else "[chunked]")
+                              "[latent, narrow form]" if kwargs.get("sink") is not None else
+                              "[two maps]" if args[2].group.v_heads != args[2].group.request.num_kv_heads else "[chunked]")
                 self.records.append((label, t0, t1) + self._cost(name, args, kwargs, out))
             return out
         return timed
@@ -568,13 +618,15 @@ def _family_arm(torch, raw, peaks, prefill_tokens, batch, context, steps, warmup
 
 
 def run_family(args) -> int:
-    """--family kudazen: the Kudazen design at a few sizes that resemble a real model's layers (random weights),
-    beside the Qwen3 decoder of the same width, feed-forward size, layer count and vocabulary.  One JSON line."""
+    """--family kudazen | nazulorn: the design at a few sizes that resemble a real model's layers (random weights), beside
+    the library's closest model of the same width, feed-forward work per token, layer count and vocabulary (Kudazen
+    beside the Qwen3 decoder, Nazulorn beside Kudazen).  One JSON line."""
     import torch
     peaks, peak_source = load_peaks()
     torch.cuda.set_device(0)
-    sizes = [s for s in (args.sizes.split(",") if args.sizes else sorted(FAMILY_SIZES)) if s]
-    result = {"family": args.family, "beside": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights",
+    table, beside_name, beside_arch = FAMILIES[args.family]
+    sizes = [s for s in (args.sizes.split(",") if args.sizes else sorted(table)) if s]
+    result = {"family": args.family, "beside": beside_arch, "dtype": "bf16", "data": "synthetic, random weights",
               "prefill_tokens": PREFILL_TOKENS, "decode_batch": args.batch, "decode_context": args.context, "steps": args.steps,
               "warmup": args.warmup, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")}, "peaks_from": peak_source,
               "timing": "CUDA events; decode through the captured graph; *_calls: one eager pass with events around every call "
@@ -582,13 +634,13 @@ def run_family(args) -> int:
               "sizes": {}}
     with ClockSampler() as clocks:
         for name in sizes:
-            if name not in FAMILY_SIZES:
-                print(f"unknown size {name!r}; known: {', '.join(sorted(FAMILY_SIZES))}", file=sys.stderr)
+            if name not in table:
+                print(f"unknown size {name!r}; known: {', '.join(sorted(table))}", file=sys.stderr)
                 return 1
-            ours, beside = FAMILY_SIZES[name]
+            ours, beside = table[name]
             result["sizes"][name] = {
-                "kudazen": _family_arm(torch, ours, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup),
-                "qwen3": _family_arm(torch, beside, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup)}
+                args.family: _family_arm(torch, ours, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup),
+                beside_name: _family_arm(torch, beside, peaks, PREFILL_TOKENS, args.batch, args.context, args.steps, args.warmup)}
     result["clocks"] = clocks.summary()
     print(json.dumps(result))
     return 0
@@ -796,8 +848,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0)
     ap.add_argument("--skip-points", action="store_true", help="leave out the further decode points")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--family", default="", choices=["", "kudazen"],
-                    help="instead of the default workload: this model family at a few layer sizes, beside the Qwen3 shape of equal size")
+    ap.add_argument("--family", default="", choices=["", "kudazen", "nazulorn"],
+                    help="instead of the default workload: this model family at a few layer sizes, beside the library's closest "
+                         "model of equal size (kudazen beside the Qwen3 shape, nazulorn beside kudazen)")
     ap.add_argument("--sizes", default="", help="with --family: sizes to run, with commas between them (default: all)")
     args = ap.parse_args()
 

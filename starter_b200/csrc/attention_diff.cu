@@ -15,9 +15,9 @@ __device__ __forceinline__ float turned(const T* src, int c, int rot, const floa
     return to_f<T>(src[c]);
 }
 
-// One block per row.  q [rows, nq heads, D] and k [rows, n_kv_heads, D] are views of wider rows (row strides in
-// elements, heads side by side); v [rows, v_heads * v_dim] likewise.  The turned queries go to q_out (contiguous), the
-// turned keys and the values to the row's place in the cache.
+// gridDim.y blocks per row share the row's heads out.  q [rows, nq heads, D] and k [rows, n_kv_heads, D] are views of
+// wider rows (row strides in elements, heads side by side); v [rows, v_heads * v_dim] likewise.  The turned queries go
+// to q_out (contiguous), the turned keys and the values to the row's place in the cache.
 template <class T>
 __global__ void rotate_half_store_kernel(const T* __restrict__ q, long long q_row, const T* __restrict__ k, long long k_row,
                                          const T* __restrict__ v, long long v_row, T* __restrict__ q_out, SbBatch batch, SbFlex p,
@@ -36,28 +36,32 @@ __global__ void rotate_half_store_kernel(const T* __restrict__ q, long long q_ro
         sn[i] = s * mag;
     }
     __syncthreads();
-    const T* qr = q + row * q_row;
-    T* qo = q_out + (long long)row * nq * D;
-    for (int e = threadIdx.x; e < nq * D; e += blockDim.x) {
-        const int h = e / D, c = e - h * D;
-        qo[e] = from_f<T>(turned<T>(qr + h * D, c, rot, cs, sn));
-    }
-    const T* kr = k + row * k_row;
-    for (int e = threadIdx.x; e < p.n_kv_heads * D; e += blockDim.x) {
-        const int h = e / D, c = e - h * D;
-        const long long tok = flex_token(p, slot, pos, h);
-        if (tok < 0) {
-            if (c == 0) atomicOr(status, SB_STATUS_NO_PAGE);
-            continue;
-        }
-        ((T*)p.k)[tok * D + c] = from_f<T>(turned<T>(kr + h * D, c, rot, cs, sn));
-    }
+    // units of work: a query head, a key head, a value head; the blocks of a row share them out
     const int vh = p.v_heads > 0 ? p.v_heads : p.n_kv_heads, per = p.n_kv_heads / vh;
-    const T* vr = v + row * v_row;
-    for (int e = threadIdx.x; e < vh * p.v_dim; e += blockDim.x) {
-        const int h = e / p.v_dim, c = e - h * p.v_dim;
-        const long long tok = flex_value_token(p, flex_token(p, slot, pos, h * per), h * per);
-        if (tok >= 0) ((T*)p.v)[tok * p.v_row + c] = vr[e];
+    const int units = nq + p.n_kv_heads + vh;
+    for (int u = blockIdx.y; u < units; u += gridDim.y) {
+        if (u < nq) {
+            const T* src = q + row * q_row + (long long)u * D;
+            T* dst = q_out + ((long long)row * nq + u) * D;
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = from_f<T>(turned<T>(src, c, rot, cs, sn));
+        } else if (u < nq + p.n_kv_heads) {
+            const int h = u - nq;
+            const long long tok = flex_token(p, slot, pos, h);
+            if (tok < 0) {
+                if (threadIdx.x == 0) atomicOr(status, SB_STATUS_NO_PAGE);
+                continue;
+            }
+            const T* src = k + row * k_row + (long long)h * D;
+            T* dst = (T*)p.k + tok * D;
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = from_f<T>(turned<T>(src, c, rot, cs, sn));
+        } else {
+            const int h = u - nq - p.n_kv_heads;
+            const long long tok = flex_value_token(p, flex_token(p, slot, pos, h * per), h * per);
+            if (tok < 0) continue;
+            const T* src = v + row * v_row + (long long)h * p.v_dim;
+            T* dst = (T*)p.v + tok * p.v_row;
+            for (int c = threadIdx.x; c < p.v_dim; c += blockDim.x) dst[c] = src[c];
+        }
     }
 }
 
@@ -91,13 +95,17 @@ int sb_rotate_half_store(int dtype, const void* q, long long q_row, const void* 
                          cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (rot < 0 || rot % 2 || rot > p.k_dim || (rot > 0 && freqs == nullptr)) return (int)cudaErrorInvalidValue;
-    const int threads = nq * p.k_dim >= 2048 ? 256 : 128;
+    const int threads = p.k_dim >= 128 || p.v_dim >= 128 ? 128 : 64;
+    const int vh = p.v_heads > 0 ? p.v_heads : p.n_kv_heads, units = nq + p.n_kv_heads + vh;
+    // few rows: a block per head, so that a decode step's rows are spread over the SMs; many rows: a few blocks per row
+    const int per_row = batch.n_rows >= 1024 ? min(units, 4) : (batch.n_rows >= 128 ? min(units, 8) : min(units, 64));
+    dim3 grid(batch.n_rows, per_row);
     const size_t smem = (size_t)rot * sizeof(float);
     if (dtype == SB_F32)
-        sb_launch(rotate_half_store_kernel<float>, batch.n_rows, threads, smem, stream, (const float*)q, q_row, (const float*)k, k_row,
+        sb_launch(rotate_half_store_kernel<float>, grid, threads, smem, stream, (const float*)q, q_row, (const float*)k, k_row,
                   (const float*)v, v_row, (float*)q_out, batch, p, freqs, rot, mag, nq, status);
     else
-        sb_launch(rotate_half_store_kernel<__nv_bfloat16>, batch.n_rows, threads, smem, stream, (const __nv_bfloat16*)q, q_row,
+        sb_launch(rotate_half_store_kernel<__nv_bfloat16>, grid, threads, smem, stream, (const __nv_bfloat16*)q, q_row,
                   (const __nv_bfloat16*)k, k_row, (const __nv_bfloat16*)v, v_row, (__nv_bfloat16*)q_out, batch, p, freqs, rot, mag, nq,
                   status);
     SB_LAUNCH_CHECK();

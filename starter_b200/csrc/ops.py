@@ -131,8 +131,9 @@ class Ops:
                                      SbFlex, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
             "sb_diff_combine": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
             "sb_gla_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
-                            c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int, c_void_p, c_void_p],
-            "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                            c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+            "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                             c_void_p],
             "sb_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_moe_gather": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
             "sb_moe_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -1016,9 +1017,13 @@ class Ops:
         if tuple(z.shape) != (rows, heads * dim) or state.shape[1] != heads * dim * vdim or norm.numel() != vdim:
             raise KernelError("gla_scan: sizes do not fit")
         y = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        # heads of more than 64 value channels: their columns are shared out over blocks, which leave raw outputs here
+        raw = torch.empty((rows, heads * vdim), dtype=torch.float32, device=q.device) if vdim > 64 else None
         self._check(self.lib.sb_gla_scan(_code(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(z), _ptr(bias), _ptr(norm),
                                          float(eps), float(tau), float(q_scale), _ptr(state), state.stride(0), self._batch(ctx),
-                                         heads, dim, vdim, _ptr(y), self._stream()), "gla_scan")
+                                         heads, dim, vdim, _ptr(y), _ptr(raw), self._stream()), "gla_scan")
+        if raw is not None:
+            self.launches += 1   # the norm and the gate
         return y
 
     def moe_route(self, h, router, correction, top, scale):
@@ -1031,8 +1036,10 @@ class Ops:
             raise KernelError("moe_route: a 32-bit router of up to 1024 outputs, up to 32 choices")
         chosen = torch.empty((rows, top), dtype=torch.int32, device=h.device)
         weight = torch.empty((rows, top), dtype=torch.float32, device=h.device)
-        self._check(self.lib.sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(chosen), _ptr(weight), rows,
-                                          width, n_out, int(top), float(scale), self._stream()), "moe_route")
+        logits = torch.empty((rows, n_out), dtype=torch.float32, device=h.device)
+        self._check(self.lib.sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(logits), _ptr(chosen),
+                                          _ptr(weight), rows, width, n_out, int(top), float(scale), self._stream()), "moe_route")
+        self.launches += 1   # logits, then the choice
         return chosen, weight
 
     MOE_PAIRS_MAX = int(os.environ.get("STARTER_B200_MOE_PAIRS_MAX", 64))   # pairs up to which every pair streams its expert

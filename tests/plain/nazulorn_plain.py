@@ -156,14 +156,15 @@ def route(h, router, correction, r):
     s = torch.softmax(h @ router.T, dim=-1)
     chosen = torch.topk(s + correction, int(r["top"]), dim=-1).indices
     picked = torch.gather(s, 1, chosen)
-    return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20) * r["scale"]
+    return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
 
 
-def expert_mixture(h, w, mlp):
-    """h [T, width]; w: the feed-forward's tensors by short name ('e3.gate', 'router', 'shared.up', ...)."""
+def expert_mixture(h, w, mlp, choice=None):
+    """h [T, width]; w: the feed-forward's tensors by short name ('e3.gate', 'router', 'shared.up', ...).  ``choice``:
+    (chosen, weights) to use instead of the router's own."""
     r = mlp["router"]
-    E, limit = int(r["experts"]), mlp["expert"]["limit"]
-    chosen, weights = route(h, w["router"], w["correction"], r)
+    E, limit = int(r["experts"]), (mlp.get("expert") or {}).get("limit")
+    chosen, weights = route(h, w["router"], w["correction"], r) if choice is None else choice
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, wt in zip(chosen[t].tolist(), weights[t]):
@@ -229,3 +230,16 @@ def forward(cfg, tensors, tokens, return_layers=False):
     x = X.sum(dim=0)
     logits = (rms_norm(x, tensors["final.norm"], eps) @ tensors["head"].T) * cfg.get("logit_scale", 1.0)
     return (logits, torch.stack(seen)) if return_layers else logits
+
+
+def generate(cfg, tensors, prompts, n_new):
+    """Greedy continuation of every prompt by ``n_new`` tokens: the whole sequence is run again for every token."""
+    out = []
+    for prompt in prompts:
+        seq, new = list(prompt), []
+        for _ in range(n_new):
+            tok = int(forward(cfg, tensors, seq)[-1].argmax())
+            new.append(tok)
+            seq.append(tok)
+        out.append(new)
+    return out
