@@ -56,7 +56,8 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 // stored.  The blend of a thread's first turn stays in registers (one turn covers rows of up to 4 * threads columns);
 // later turns read their columns again (still in L1).
 template <class T, class W, int S, int VW>
-__global__ void stream_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mix,
+__global__ void __launch_bounds__(512)
+stream_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mix,
                                    const float* __restrict__ out_w, const float* __restrict__ read_w, const W* __restrict__ weight,
                                    T* __restrict__ n, int width, float eps) {
     __shared__ float red[33];
@@ -173,7 +174,7 @@ int sb_stream_norm(int dtype, int w_dtype, float* x, const void* y, const float*
     if (y == nullptr && read_w == nullptr) return 0;
     const bool vec = width % 4 == 0;
     const int cols = vec ? width / 4 : width;
-    const int threads = cols >= 512 ? 512 : (cols >= 256 ? 256 : 128);
+    const int threads = cols >= 512 && streams <= 4 ? 512 : (cols >= 256 ? 256 : 128);   // many streams: many registers per thread
     typedef __nv_bfloat16 bf;
 #define SB_SN(T, W, S)                                                                                                              \
     do {                                                                                                                            \
