@@ -17,6 +17,27 @@
 
 __device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
 
+// n values of the run's type into shared memory as floats; bfloat16 rows whose width is a multiple of 8 go 16 bytes a read.
+template <class T> __device__ __forceinline__ void stage_rows(float* dst, const T* src, int n, bool vec) {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < n; e += blockDim.x) dst[e] = to_f<T>(src[e]);
+}
+template <> __device__ __forceinline__ void stage_rows<__nv_bfloat16>(float* dst, const __nv_bfloat16* src, int n, bool vec) {
+    if (!vec || (reinterpret_cast<uintptr_t>(src) & 15)) {
+#pragma unroll 8
+        for (int e = threadIdx.x; e < n; e += blockDim.x) dst[e] = __bfloat162float(src[e]);
+        return;
+    }
+#pragma unroll 4
+    for (int e = threadIdx.x * 8; e < n; e += blockDim.x * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + e);
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(hh[0]), b = __bfloat1622float2(hh[1]), c = __bfloat1622float2(hh[2]), d = __bfloat1622float2(hh[3]);
+        *reinterpret_cast<float4*>(dst + e) = make_float4(a.x, a.y, b.x, b.y);
+        *reinterpret_cast<float4*>(dst + e + 4) = make_float4(c.x, c.y, d.x, d.y);
+    }
+}
+
 // Router logits, 32-bit.  A block of 8 warps takes R rows (R <= 8) and 8 router rows: the rows of h are staged in shared
 // memory as floats, warp w reads router row blockIdx.y * 8 + w once (16 bytes per lane where the width allows, four
 // turns in flight) and forms its dot product with all R rows.  With few rows R is 1 and the router's rows are spread
@@ -31,11 +52,9 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ router, flo
     pdl_wait();
     const int row0 = blockIdx.x * R, nr = min(R, rows - row0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll 8
-    for (int e = threadIdx.x; e < nr * width; e += blockDim.x) hs[e] = to_f<T>(h[(long long)row0 * width + e]);
+    stage_rows<T>(hs, h + (long long)row0 * width, nr * width, (width & 7) == 0);
     __syncthreads();
-    const int e = blockIdx.y * 8 + warp;
-    if (e >= n_out) return;
+    for (int e = blockIdx.y * 8 + warp; e < n_out; e += gridDim.y * 8) {
     const float* wr = router + (long long)e * width;
     float acc[MOE_ROUTE_ROWS];
 #pragma unroll
@@ -65,6 +84,7 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ router, flo
             const float d = warp_sum(acc[r]);
             if (lane == 0) logits[(long long)(row0 + r) * n_out + e] = d;
         }
+    }
 }
 
 // One warp per row: softmax over all outputs, the `top` largest of score + correction (of equals the lowest index), and
@@ -210,8 +230,8 @@ __device__ __forceinline__ void dot2<__nv_bfloat16>(const float* xs, const __nv_
         }
         return;
     }
-#pragma unroll 2
-    for (int i = lane * 8; i < n; i += 256) {
+#pragma unroll 4
+    for (int i = lane * 8; i < n; i += 256) {   // unrolled: eight 16-byte reads of the matrix in flight per lane
         const uint4 a = *reinterpret_cast<const uint4*>(r0 + i);
         uint4 b = make_uint4(0u, 0u, 0u, 0u);
         if (r1 != nullptr) b = *reinterpret_cast<const uint4*>(r1 + i);
@@ -241,7 +261,7 @@ moe_pair_gate_up_kernel(const T* __restrict__ h, const int* __restrict__ chosen,
     const int e = chosen[pair];
     if (e < 0 || e >= n_experts) return;
     const T* hr = h + (long long)(pair / top) * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) pair_x[i] = to_f<T>(hr[i]);
+    stage_rows<T>(pair_x, hr, width, (width & 7) == 0);
     __syncthreads();
     const T* wg = w_gate_up + (long long)e * 2 * ff * width;
     for (int c = blockIdx.y * n_warps + warp; c < ff; c += gridDim.y * n_warps) {
@@ -268,7 +288,7 @@ moe_pair_down_kernel(const T* __restrict__ act, const int* __restrict__ chosen, 
     const int e = chosen[pair];
     if (e < 0 || e >= n_experts) return;
     const T* ar = act + (long long)pair * ff;
-    for (int i = threadIdx.x; i < ff; i += blockDim.x) pair_x[i] = to_f<T>(ar[i]);
+    stage_rows<T>(pair_x, ar, ff, (ff & 7) == 0);
     __syncthreads();
     const T* wd = w_down + (long long)e * width * ff;
     for (int c = 2 * (blockIdx.y * n_warps + warp); c < width; c += 2 * gridDim.y * n_warps) {
@@ -364,7 +384,9 @@ int sb_moe_route(int dtype, const void* h, const float* router, const float* cor
     while (R > 1 && (size_t)R * width * sizeof(float) > 96 * 1024) R >>= 1;
     const size_t smem = (size_t)R * width * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned int)((rows + R - 1) / R), (unsigned int)((n_out + 7) / 8));
+    // one row per block: the router's rows are spread over blocks of eight; several rows: a block stages them once and
+    // its warps walk all the router's rows
+    dim3 grid((unsigned int)((rows + R - 1) / R), R == 1 ? (unsigned int)((n_out + 7) / 8) : 1u);
 #define SB_ROUTE(T)                                                                                                              \
     do {                                                                                                                         \
         if (smem > 48 * 1024) {                                                                                                  \
@@ -407,7 +429,7 @@ int sb_moe_pairs(int dtype, const void* h, const int* chosen, const void* w_gate
     if (n_pairs <= 0 || n_experts <= 0) return 0;
     const int threads = 256, warps = threads / 32;
     // enough blocks along the columns for a few per SM when the pairs are few
-    const int want = n_pairs >= 592 ? 1 : (592 + n_pairs - 1) / n_pairs;
+    const int want = n_pairs >= 1184 ? 1 : (1184 + n_pairs - 1) / n_pairs;   // eight blocks of eight warps per SM
     dim3 g1(n_pairs, (unsigned int)max(1, min(want, (ff + warps - 1) / warps)));
     dim3 g2(n_pairs, (unsigned int)max(1, min(want, (width + 2 * warps - 1) / (2 * warps))));
     const size_t s1 = (size_t)width * sizeof(float), s2 = (size_t)ff * sizeof(float);

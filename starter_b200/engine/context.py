@@ -107,6 +107,9 @@ class ResidualStream:
         return out
 
 
+_ONES: Dict[Any, torch.Tensor] = {}
+
+
 class StreamResidual:
     """A residual kept in ``streams`` 32-bit copies side by side, x [rows, streams * hidden].  A branch's output y
     returns as X'_t = sum_s mix[s, t] X_s + out[t] * y; the return waits here (``pending`` = (y, mix, out)) and is
@@ -128,7 +131,10 @@ class StreamResidual:
 
     def normed(self, norm) -> torch.Tensor:
         """The norm of the sum of the streams (what the output head reads)."""
-        ones = torch.ones(self.streams, dtype=torch.float32, device=self.x.device)
+        key = (self.x.device, self.streams)
+        ones = _ONES.get(key)
+        if ones is None:   # kept: a step makes no tensor it does not need
+            ones = _ONES[key] = torch.ones(self.streams, dtype=torch.float32, device=self.x.device)
         return self.read(norm.ops, ones, norm.weight, norm.eps, norm.dtype)
 
     def at_rows(self, ops, rows: torch.Tensor) -> "StreamResidual":
