@@ -329,7 +329,8 @@ def moe_plain(s, w, h, choice=None):
 
 MOE_SIZES = [dict(width=72, E=5, I=2, top=3, ff=40, limit=0.8, shared=(56, 1.2)), dict(width=128, E=4, I=0, top=1, ff=72, limit=2.0),
              dict(width=40, E=2, I=3, top=4, ff=24, limit=0.5, shared=(16, 3.0)), dict(width=64, E=0, I=3, top=2, ff=8, limit=1.0),
-             dict(width=256, E=40, I=1, top=8, ff=64, limit=1.0, shared=(128, 1.0))]
+             dict(width=256, E=40, I=1, top=8, ff=64, limit=1.0, shared=(128, 1.0)),
+             dict(width=36, E=3, I=1, top=2, ff=20, limit=1.0, shared=(12, 1.0))]      # rows that 16-byte reads do not fit
 
 
 @pytest.mark.parametrize("mode", MODES)
@@ -440,3 +441,43 @@ def test_captured_decoding_gives_the_tokens_of_eager_decoding_bfloat16(folders):
     eager = Engine(folders["B"], dtype="bfloat16", max_batch=4, max_context=256, use_graphs=False).generate_all(prompts, 40)
     captured = Engine(folders["B"], dtype="bfloat16", max_batch=4, max_context=256, use_graphs=True).generate_all(prompts, 40)
     assert eager == captured
+
+
+def test_replay_through_the_trace_runner_and_generation_from_the_command_line(folders, tmp_path):
+    """bin/trace_run as a user drives it (a prompt in two portions, then two requests decoded in one batch, logits in
+    files), and ``python -m starter_b200 generate`` on the same folder."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    folder, vocab = folders["A"], 211
+    a, b = random_tokens(vocab, (75, 9), seed=12)
+    ref = cases.plain_logits(folder, [a, b])
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[40:70], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": b[:4], "want": [3]}], "end": []}]
+    for t in range(5):
+        steps.append({"step": 3 + t, "entries": [{"id": "a", "tokens": [a[70 + t]], "want": [0]}, {"id": "b", "tokens": [b[4 + t]], "want": [0]}],
+                      "end": ["a", "b"] if t == 4 else []})
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out",
+                           str(tmp_path), "--max-tokens", "256"], input="".join(json.dumps(s) + "\n" for s in steps),
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    read = lambda n: torch.from_numpy(np.fromfile(tmp_path / f"{n}.f32", dtype="<f4").reshape(-1, vocab).copy())
+    tol = 1e-4 * float(ref[0].abs().max())
+    assert float((read(0) - ref[0][[0, 39]]).abs().max()) <= tol and not (tmp_path / "1.f32").exists()
+    assert float((read(2) - ref[1][[3]]).abs().max()) <= tol
+    for t in range(5):
+        assert float((read(3 + t) - torch.stack([ref[0][70 + t], ref[1][4 + t]])).abs().max()) <= tol, f"decoded token {t}"
+    cfg, tensors = plain.read_folder(folder)
+    want = plain.generate(cfg, tensors, [a[:6], b[:3]], 4)
+    proc = subprocess.run([sys.executable, "-m", "starter_b200", "generate", "--model", str(folder), "--dtype", "float32", "--input-ids",
+                           ",".join(map(str, a[:6])) + ";" + ",".join(map(str, b[:3])), "--max-new-tokens", "4", "--max-batch", "4",
+                           "--max-context", "128"],
+                          capture_output=True, text=True, timeout=600, cwd=str(root))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [json.loads(line) for line in proc.stdout.splitlines()] == want
