@@ -493,7 +493,12 @@ class TimedOps:
                 cache_bytes = ctx.n_seqs * reach * token_bytes
             else:
                 t = ctx.n_rows / ctx.n_seqs
-                pairs = ctx.n_seqs * (t * (t + 1) / 2.0 if reach >= t else t * reach / 2.0)
+                if reach >= t:
+                    pairs = ctx.n_seqs * t * (t + 1) / 2.0
+                elif kwargs.get("chunk") and reach == kwargs.get("chunk"):
+                    pairs = ctx.n_seqs * t * reach / 2.0                                  # blocks of `chunk` positions, each causal inside
+                else:
+                    pairs = ctx.n_seqs * (reach * (reach + 1) / 2.0 + (t - reach) * reach)   # a sliding window: full reach from position `reach` on
                 cache_bytes = ctx.n_rows * token_bytes
             flops = 2.0 * pairs * heads * (req.head_dim + v_dim)
             nbytes = cache_bytes + 2 * self._nbytes([q]) if name != "qk_attention" else cache_bytes + self._nbytes([q])
