@@ -62,17 +62,15 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     for (int t0 = row0; t0 < row1; t0 += GLA_TB) {
         const int nt = min(GLA_TB, row1 - t0);
         __syncthreads();
-#pragma unroll 2
-        for (int e = tid; e < nt * D; e += n_threads) {
-            const int tt = e / D, i = e - tt * D;
+#pragma unroll 4
+        for (int e = tid; e < nt * D; e += n_threads) {   // unrolled: the loads of four turns are in flight together
+            const int tt = EXACT ? e / (8 * EMAX) : e / D, i = e - tt * D;   // an exact head size divides by a constant
             const long long at = (long long)(t0 + tt) * ld + head * D + i;
             qs[e] = to_f<T>(q[at]) * q_scale;
             ks[e] = to_f<T>(k[at]);
             as[e] = z[(long long)(t0 + tt) * H * D + head * D + i];
         }
-#pragma unroll 1
-        for (int e = tid; e < nt * D; e += n_threads) as[e] = decay_of(as[e] + bs[e % D], inv_tau);   // the thread's own entries
-#pragma unroll 2
+#pragma unroll 4
         for (int e = tid; e < nt * nv; e += n_threads) {
             const int tt = e / nv, c = e - tt * nv;
             const long long at = (long long)(t0 + tt) * ld + head * V + j0 + c;
@@ -82,25 +80,34 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 gs[tt * GLA_VB + c] = gv / (1.0f + expf(-gv));
             }
         }
+#pragma unroll 1
+        for (int e = tid; e < nt * D; e += n_threads) as[e] = decay_of(as[e] + bs[EXACT ? e % (8 * EMAX) : e % D], inv_tau);   // the thread's own entries
         __syncthreads();
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float vj = col ? vs[tt * GLA_VB + jl] : 0.f;
             float o = 0.f;
-            if (EXACT) {
+            if (EXACT) {   // two entries of the state per instruction (fma.rn.f32x2): the time here is the instruction count
+                constexpr int DC = 8 * EMAX;
+                const float2 v2 = make_float2(vj, vj), zero = make_float2(0.f, 0.f);
+                float2 o2 = zero;
 #pragma unroll
                 for (int e = 0; e < EMAX; e += 4) {
-                    const int at = tt * D + ((e >> 2) * GLA_IG + ig) * 4;
+                    const int at = tt * DC + ((e >> 2) * GLA_IG + ig) * 4;
                     const float4 q4 = *reinterpret_cast<const float4*>(qs + at);
                     const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
                     const float4 a4 = *reinterpret_cast<const float4*>(as + at);
-                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        S[e + u] = fmaf(aa[u], S[e + u], kk[u] * vj);
-                        o = fmaf(qq[u], S[e + u], o);
-                    }
+                    float2 s01 = make_float2(S[e], S[e + 1]), s23 = make_float2(S[e + 2], S[e + 3]);
+                    s01 = fma_pair(make_float2(a4.x, a4.y), s01, fma_pair(make_float2(k4.x, k4.y), v2, zero));
+                    s23 = fma_pair(make_float2(a4.z, a4.w), s23, fma_pair(make_float2(k4.z, k4.w), v2, zero));
+                    o2 = fma_pair(make_float2(q4.x, q4.y), s01, o2);
+                    o2 = fma_pair(make_float2(q4.z, q4.w), s23, o2);
+                    S[e] = s01.x;
+                    S[e + 1] = s01.y;
+                    S[e + 2] = s23.x;
+                    S[e + 3] = s23.y;
                 }
+                o = o2.x + o2.y;
             } else {
                 const float* qt = qs + tt * D + i0;
                 const float* kt = ks + tt * D + i0;
