@@ -422,12 +422,12 @@ FAMILY_SIZES = {
 def _nazulorn_raw(width, layers, gla, attention, experts, expert_ff, top, identity, shared_ff, vocab=32000, streams=2):
     """A Nazulorn configuration of ``layers`` layers that cycle through gla, attention, attention."""
     kinds = [
-        {"type": "gla", "mixer": dict(gla, tau=16.0)},
-        {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5, diff=0.6,
-                                            rot={"base": 1000000.0, "dims": attention["dim"],
-                                                 "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}})},
+        {"type": "gla", "mixer": dict(gla, tau=8.0)},
+        {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5, diff=0.5,
+                                            rot={"base": 500000.0, "dims": attention["dim"],
+                                                 "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}})},
     ]
-    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5},
+    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.0},
            "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
     entries = [dict(kinds[min(i % 3, 1)], mlp=mlp) for i in range(layers)]
     return {"architecture": "Nazulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
@@ -441,10 +441,10 @@ def _nazulorn_raw(width, layers, gla, attention, experts, expert_ff, top, identi
 NAZULORN_SIZES = {
     "1024": (_nazulorn_raw(1024, 6, dict(heads=8, dim=64, vdim=128, decay_rank=64),
                            dict(heads=8, kv_heads=2, dim=64, vdim=64, mask={"size": 1024}), experts=16, expert_ff=512, top=4,
-                           identity=4, shared_ff=2048), FAMILY_SIZES["1024"][0]),
+                           identity=2, shared_ff=2048), FAMILY_SIZES["1024"][0]),
     "2048": (_nazulorn_raw(2048, 6, dict(heads=16, dim=64, vdim=128, decay_rank=64),
                            dict(heads=8, kv_heads=4, dim=128, vdim=128, mask={"size": 2048}), experts=32, expert_ff=1024, top=4,
-                           identity=4, shared_ff=4096), FAMILY_SIZES["2048"][0]),
+                           identity=2, shared_ff=4096), FAMILY_SIZES["2048"][0]),
 }
 FAMILIES = {"kudazen": (FAMILY_SIZES, "qwen3", "Qwen3ForCausalLM"), "nazulorn": (NAZULORN_SIZES, "kudazen", "Kudazen")}
 

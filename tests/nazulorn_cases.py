@@ -71,8 +71,8 @@ CASES = {
     # streams, one chosen expert and no identity outputs, state heads of 64 x 64 and 32 x 128
     "B": _model(300, 128, 1e-6, [
         _with(_gla(2, 64, 64, 16.0, 16), _B_MOE),
-        _with(_attention(4, 2, 32, 64, window=64, dims=32, base=1e6, scaling=(4.0, 256, 32.0, 1.0), diff=0.6), _B_MOE),
-        _with(_attention(2, 1, 64, 128, window=100, dims=32, diff=0.2), _moe(3, 1, 2, 2.5, 64, 1.0, shared=(128, 1.0))),
+        _with(_attention(8, 2, 32, 64, window=64, dims=32, base=2e5, scaling=(6.0, 256, 16.0, 2.0), diff=0.45), _B_MOE),
+        _with(_attention(2, 1, 64, 128, window=100, dims=32, diff=0.2), _moe(3, 1, 2, 1.9, 80, 1.1, shared=(96, 0.9))),
         _with(_gla(1, 32, 128, 4.0, 8), _B_MOE)], streams=4, mult=0.3, embed=0.5, logit=2.0),
     # a plain residual (no streams), single heads, widths that are no multiples of 8, no window, nothing turned, a state
     # head of 40 x 72, more choices than real experts

@@ -163,7 +163,7 @@ def diff_entry(s):
 
 DIFF_SIZES = [
     dict(H=6, G=2, D=16, V=24, window=20, dims=8, scaling=(8.0, 16.0, 4.0, 1.0), diff=0.3),     # the general kernel
-    dict(H=4, G=2, D=32, V=64, window=64, dims=32, scaling=(4.0, 256.0, 32.0, 1.0), diff=0.6),   # the tensor-core kernels, a window of one page
+    dict(H=8, G=2, D=32, V=64, window=64, dims=32, scaling=(6.0, 256.0, 16.0, 2.0), diff=0.45),  # the tensor-core kernels, a window of one page
     dict(H=2, G=1, D=64, V=128, window=100, dims=32),                                           # part of a map turns
     dict(H=1, G=1, D=20, V=12, window=None, dims=0, diff=0.8),                                  # no window, nothing turned
     dict(H=8, G=4, D=128, V=128, window=70, dims=128, base=1e6),
@@ -206,13 +206,13 @@ def test_query_rows_are_reordered_by_key_head_and_map():
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("window, loud", [(40, 24), (40, 25), (64, 0), (64, 1), (7, 57), (7, 58), (100, 30), (None, 2)])
+@pytest.mark.parametrize("window, loud", [(48, 16), (48, 17), (64, 0), (64, 1), (7, 57), (7, 58), (100, 30), (None, 2)])
 def test_a_loud_key_at_the_window_edge(mode, window, loud):
     """One token's input is many times larger than the others', so its key takes a map's whole softmax wherever that
     map's score with it is positive: a window that is one position off shows at once.  The queries just inside and just
     outside the window stand at page borders and inside pages, in a prompt and decoded one by one."""
     rt = runtime(mode)
-    spec = diff_spec(H=4, G=2, D=32, V=64, window=window, dims=32)
+    spec = diff_spec(H=8, G=4, D=32, V=64, window=window, dims=32)
     w = diff_weights(spec, 40)
     part = build_part("mixer", spec, {k: v.to(rt.dtype).cuda() for k, v in w.items()}, rt)
     n = 420 if window is None else loud + window + 12
@@ -329,7 +329,7 @@ def moe_plain(s, w, h, choice=None):
 
 MOE_SIZES = [dict(width=72, E=5, I=2, top=3, ff=40, limit=0.8, shared=(56, 1.2)), dict(width=128, E=4, I=0, top=1, ff=72, limit=2.0),
              dict(width=40, E=2, I=3, top=4, ff=24, limit=0.5, shared=(16, 3.0)), dict(width=64, E=0, I=3, top=2, ff=8, limit=1.0),
-             dict(width=256, E=40, I=1, top=8, ff=64, limit=1.0, shared=(128, 1.0)),
+             dict(width=256, E=40, I=1, top=8, ff=64, limit=1.0, shared=(96, 1.3)),
              dict(width=36, E=3, I=1, top=2, ff=20, limit=1.0, shared=(12, 1.0))]      # rows that 16-byte reads do not fit
 
 
